@@ -1,0 +1,325 @@
+#!/usr/bin/env python
+"""Headline benchmark: VGG-16 forward inference, global batch 256, fp32 semantics
+with TF32 tensor-core contractions, on N B200 GPUs of one node.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+                    [--workload vgg16|alexnet|resnet50|lstm2] [--math tf32|tf32x3|fp32]
+
+A step is one forward pass of the whole network over the batch (each rank runs
+its contiguous slice with replicated weights; for N>1 the step ends with the one
+collective of the path, an NCCL all-gather of the logits).  `value` is images/s
+with the batch resident in HBM; `e2e` is the same metric through the C-ABI host
+call (pinned host batch copied in, probabilities copied out, every step).
+Inputs and weights are seeded synthetic tensors with ImageNet shapes and value
+range (uniform [0,1) images, He-normal weights).
+
+`--impl reference` times the reference's own CPU implementation (the binary
+under oracle/_ref, compiled from the reference sources) on a bounded sample of
+the same workload on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+WEIGHT_SEED, INPUT_SEED = 3000, 3001
+UNIT = {"vgg16": "images/s", "alexnet": "images/s", "resnet50": "images/s", "lstm2": "sequences/s"}
+DEFAULT_BATCH = {"vgg16": 256, "alexnet": 16, "resnet50": 256, "lstm2": 64}
+CPU_SAMPLE = {"vgg16": 8, "alexnet": 16, "resnet50": 16, "lstm2": 8}     # units per CPU-baseline forward
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return dict(hbm_gbs=d["hbm_gbs"], bf16_burst=d["bf16_tflops"], bf16_sustained=d["bf16_tflops_sustained"],
+                    source="measured")
+    return dict(hbm_gbs=6650.0, bf16_burst=1590.0, bf16_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.gpu)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [t.strip() for t in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def make_workload(name: str, batch: int):
+    from nebula_b200 import workloads
+    return workloads.WORKLOADS[name](batch=batch)
+
+
+# ----------------------------------------------------------------- CPU baseline
+def run_cpu_reference(wl_name: str, reps: int, warm: int):
+    """Times network_t::forward() of the compiled reference (OpenBLAS build, all
+    host cores) on a bounded sample of the workload.  Returns a dict or raises."""
+    import numpy as np
+    from oracle import oracle as O
+    flavour = "oblas" if O.ref_binary("oblas") else ("custom" if O.ref_binary("custom") else None)
+    sample = CPU_SAMPLE[wl_name]
+    wl = make_workload(wl_name, sample)
+    cores = os.cpu_count() or 1
+    w = wl.make_weights(WEIGHT_SEED)
+    x = wl.make_input(INPUT_SEED)
+    if flavour is None:
+        # no compiled reference on this machine: time the plain-C restatement instead
+        O.lib().nbo_set_threads(min(cores, 64))
+        times = []
+        for _ in range(warm + reps):
+            t0 = time.perf_counter()
+            O.forward_network(wl.cfg, w, x)
+            times.append((time.perf_counter() - t0) * 1e3)
+        kind, used = "port", min(cores, 64)
+    else:
+        _, info = O.run_reference(wl.cfg, w, x, recurrent=wl.recurrent, flavour=flavour, threads=min(cores, 64),
+                                  reps=warm + reps)
+        times = info["forward_ms"]
+        kind, used = "reference", info["threads"]
+    timed = times[warm:]
+    ms = statistics.median(timed)
+    return dict(value=sample / (ms / 1e3), ms_per_step=ms, cores=used, kind=kind,
+                sample=f"{sample} {wl.unit} of {wl_name} per forward, median of {len(timed)} timed forward() calls "
+                       f"after {warm} warm-up, {'OpenBLAS 0.3.15' if flavour == 'oblas' else 'in-tree GEMM'} build",
+                unit=UNIT[wl_name])
+
+
+def reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    wl_name = args.workload
+    batch = args.batch or DEFAULT_BATCH[wl_name]
+    try:
+        r = run_cpu_reference(wl_name, max(1, args.steps), max(0, args.warmup))
+    except Exception as e:  # the checker could not be built or run here
+        print(json.dumps({"impl": "reference", "unavailable": f"{type(e).__name__}: {e}"[:300]}))
+        return
+    line = {
+        "impl": "reference", "metric": f"{wl_name} forward inference throughput", "value": round(r["value"], 3),
+        "unit": r["unit"], "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(r["ms_per_step"], 3), "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{wl_name}_b{batch}", "global_batch": batch, "note": "reference CPU path on host cores"},
+        "cpu_baseline": {"value": round(r["value"], 3), "unit": r["unit"], "cores": r["cores"], "kind": r["kind"],
+                         "sample": r["sample"]},
+        "e2e": {"value": round(r["value"], 3), "unit": r["unit"], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+# --------------------------------------------------------------------- GPU arm
+def gpu_arm(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from nebula_b200 import api, sharding
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+
+    wl_name = args.workload
+    batch = args.batch or DEFAULT_BATCH[wl_name]
+    lo, hi = sharding.shard_bounds(batch, world, rank)
+    my = hi - lo
+    if my == 0:
+        raise SystemExit(f"rank {rank} has no units: global batch {batch} < world size {world}")
+    full = make_workload(wl_name, batch)
+    wl = full.with_batch(my)
+
+    handle = api.Handle(local, args.math)
+    net = api.Network(handle, wl.cfg)
+    weights = full.make_weights(WEIGHT_SEED)
+    net.load_weights(weights)
+    del weights
+    x_host_full = full.make_input(INPUT_SEED)
+    x_host = sharding.shard_input(x_host_full, world, rank, full.recurrent)
+    del x_host_full
+    x_dev = torch.from_numpy(x_host).to(dev)
+    x_pin = torch.from_numpy(x_host).pin_memory()
+    out_pin = torch.empty(net.output_size, dtype=torch.float32).pin_memory()
+    classes = full.classes
+    rows = net.logits_size // classes
+
+    def step_device():
+        net.forward(x_dev)
+        if world > 1:
+            lg = net.logits(device=dev).view(rows, classes)
+            if full.recurrent:
+                sharding.gather_time_major(lg.view(-1, my, classes), batch, world, rank)
+            else:
+                sharding.gather_rows(lg, batch, world, rank)
+
+    def step_host():
+        net.forward_host(x_pin, out_pin)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    W, K = max(3, args.warmup), max(1, args.steps)
+    for _ in range(W):
+        step_device()
+    handle.synchronize()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = handle.launch_count()
+    handle.profile_begin()
+    total_ms = timed(step_device, K)
+    prof = handle.profile_end()
+    launches = handle.launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    handle.synchronize()
+
+    for _ in range(2):
+        step_host()
+    e2e_ms = timed(step_host, K)
+    handle.synchronize()
+
+    if world > 1:
+        t = torch.tensor([float(launches)], device=dev, dtype=torch.float64)
+        dist.all_reduce(t)
+        launches = int(t.item())
+
+    if rank == 0:
+        peaks = measured_peaks()
+        ms_per_step = total_ms / K
+        value = batch / (ms_per_step / 1e3)
+        e2e = batch / (e2e_ms / K / 1e3)
+        # dominant kernel: the tcgen05 contraction (all convolutions with C >= 32 and the FC layers)
+        tf32_peak = peaks["bf16_sustained"] / 2.0
+        if args.math == "tf32x3":
+            tf32_peak /= 3.0
+        achieved = prof["tc_flops"] / (prof["tc_ms"] / 1e3) / 1e12 if prof["tc_ms"] > 0 else 0.0
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            try:
+                cpu = run_cpu_reference(wl_name, 2, 1)
+                cpu = {"value": round(cpu["value"], 3), "unit": cpu["unit"], "cores": cpu["cores"], "kind": cpu["kind"],
+                       "sample": cpu["sample"]}
+            except Exception as e:
+                cpu = {"value": None, "unit": UNIT[wl_name], "cores": 0, "kind": "port",
+                       "sample": f"unavailable: {type(e).__name__}: {e}"[:200]}
+        line = {
+            "metric": f"{wl_name} forward inference throughput", "value": round(value, 2), "unit": UNIT[wl_name],
+            "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": round(ms_per_step, 4),
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": {"tf32": "tf32", "tf32x3": "3xtf32", "fp32": "f32"}[args.math], "data": "synthetic",
+            "config": {"workload": f"{wl_name}_b{batch}", "global_batch": batch, "per_gpu_batch": my,
+                       "parallelism": f"batch-sharded replicas x{world}, logits all-gather" if world > 1 else "single GPU",
+                       "l2": "inputs and activations larger than L2 (no flush needed)",
+                       "storage": "fp32, NHWC internal"},
+            "e2e": {"value": round(e2e, 2), "unit": UNIT[wl_name], "h2d_bytes_per_step": int(x_pin.numel() * 4 * world),
+                    "d2h_bytes_per_step": int(out_pin.numel() * 4 * world)},
+            "gpu_launches": launches,
+            "clocks": clocks,
+            "roofline": {"bound": "tensor", "achieved": round(achieved, 2), "peak": round(tf32_peak, 1), "unit": "TFLOP/s",
+                         "frac": round(achieved / tf32_peak, 4) if tf32_peak else None, "traffic": None,
+                         "kernel": "gemm_tf32_tcgen05_kernel",
+                         "launches_per_step": prof["tc_launches"] / K, "kernel_ms_per_step": round(prof["tc_ms"] / K, 4),
+                         "peak_source": f"{peaks['source']}: bf16 cuBLAS sustained {peaks['bf16_sustained']} TFLOP/s / 2 "
+                                        "(dense TF32 rate is half the bf16 rate)" + (" / 3 products" if args.math == "tf32x3" else ""),
+                         "other_contraction_ms_per_step": round(prof["simt_ms"] / K, 4)},
+        }
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+        print(json.dumps(line), flush=True)
+    net.close()
+    handle.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="nebula_b200", choices=["nebula_b200", "reference"])
+    ap.add_argument("--workload", default="vgg16", choices=list(UNIT))
+    ap.add_argument("--batch", type=int, default=0, help="global batch (default: the benchmark configuration's)")
+    ap.add_argument("--math", default="tf32", choices=["tf32", "tf32x3", "fp32"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+    else:
+        gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,629 @@
+// Tensor-core GEMM / implicit-GEMM convolution for sm_100a.
+//
+//   D[M,N] = A[M,K] * B[N,K]^T   (both operands K-major, fp32 storage, TF32 math,
+//                                 fp32 accumulation in tensor memory)
+//
+// Replaces the reference's per-image im2col + SGEMM pair
+// (models/layers/convolutional_layer.cu:47-70, common/utils.cu:34-74) and its
+// fully-connected SGEMM (models/layers/connected_layer.cu:21-38) with ONE
+// persistent kernel over the whole batch:
+//   * rows of A are output pixels (image, oh, ow); the im2col matrix is never
+//     materialised -- for every filter tap (kh,kw) and 32-channel slice a TMA
+//     box load fetches the shifted NHWC window, out-of-bounds coordinates give
+//     the zero padding;
+//   * columns of D are filters; B is the weight tensor re-laid out once as
+//     [tap][filter][channel];
+//   * tcgen05.mma (kind::tf32, M=128, N=BLOCK_N, K=8) accumulates into TMEM,
+//     double-buffered so the epilogue of tile i overlaps the main loop of i+1;
+//   * the epilogue applies folded batch-norm scale/shift + bias, an optional
+//     addend (residual / LSTM input projection), the activation, and optional
+//     TF32 rounding for the next contraction, and stores NHWC rows directly.
+// A plain row-major matrix is the special case "image of height 1, 1x1 filter".
+//
+// Warp roles (192 threads; 320 in three-pass mode):
+//   warp 0      TMA producer (one elected lane)
+//   warp 1      TMEM allocation + MMA issue (one elected lane)
+//   warps 2-5   epilogue (TMEM -> registers -> global)
+//   warps 6-9   three-pass mode only: split each A tile into hi/lo TF32 terms
+//
+// Every wait is bounded: a wait that runs out sets the CTA's abort flag and the
+// device status word, all roles drain, TMEM is freed and the kernel returns.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <algorithm>
+#include <cstring>
+
+#include "device_math.cuh"
+#include "nb_internal.h"
+
+namespace nb {
+
+namespace {
+
+constexpr int BLOCK_M = 128;
+constexpr int BLOCK_K = 32;                  // fp32 elements = one 128-byte swizzle row
+constexpr int UMMA_K = 8;                    // tf32
+constexpr int A_STAGE_BYTES = BLOCK_M * BLOCK_K * 4;   // 16 KiB
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;  // ~2 s at 2 GHz
+
+struct TcParams {
+    CUtensorMap tm_a;
+    CUtensorMap tm_b;
+    CUtensorMap tm_b_lo;
+    CUtensorMap tm_y;
+    // tiling of the M dimension into (bw x bh x bn) boxes of output pixels
+    int bw, bh, bn;
+    int tiles_w, tiles_h, tiles_n;
+    int OW, OH, NB;
+    int ksize, stride, pad;
+    int c_blocks;               // 32-channel slices per tap
+    int num_k_blocks;           // ksize*ksize*c_blocks
+    int m_tiles, n_tiles;
+    int N;                      // valid output columns
+    int tx_bytes_a;             // bytes one A box load delivers
+    // epilogue
+    const float *scale, *shift, *addend;
+    long ld_addend;
+    int act, round_out;
+    float *y;
+    long ldy;
+    int tma_store;              // y meets TMA's rules: tiles leave through tm_y; else plain stores
+    int *status;
+};
+
+// ------------------------------------------------------------------ PTX glue
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false when the CTA is aborting (this wait or another ran out).
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status) {
+    if (mbar_try_wait(bar, parity)) return true;
+    long long t0 = clock64();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 32; i++)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+            *abort_flag = 1;
+            atomicExch(status, (int)DEV_TIMEOUT);
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
+}
+
+__device__ __forceinline__ void tma_load_4d(void *dst, const CUtensorMap *tm, uint64_t *bar, int c0, int c1, int c2,
+                                            int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(tm), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *tm, uint64_t *bar, int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(tm), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap *tm, const void *src, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                 ::"l"(tm), "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void tma_store_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void epilogue_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+// AND-vote across the 128 epilogue threads (named barrier 1), so that leaving the tile
+// loop is a uniform decision and no thread is left alone at a later bar.sync.
+__device__ __forceinline__ bool epilogue_all(bool pred) {
+    uint32_t r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.b32 p, %1, 0;\n\t"
+        "bar.red.and.pred q, 1, 128, p;\n\t"
+        "selp.b32 %0, 1, 0, q;\n\t}"
+        : "=r"(r)
+        : "r"((uint32_t)pred)
+        : "memory");
+    return r != 0;
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows 128 B
+// apart, 8-row groups 1024 B apart (bits: start>>4 [0,14), LBO>>4 [16,30),
+// SBO>>4 [32,46), version=1 [46,48), layout=SWIZZLE_128B(2) [61,64)).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// Instruction descriptor for kind::tf32: D=f32 (bits 4-5 = 1), A=B=tf32 (bits
+// 7-9, 10-12 = 2), both K-major (bits 15,16 = 0), N>>3 at bit 17, M>>4 at bit 24.
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
+    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+template <int BLOCK_N, bool THREE>
+struct Cfg {
+    static constexpr int B_STAGE_BYTES = BLOCK_N * BLOCK_K * 4;
+    static constexpr int STAGE_BYTES = (A_STAGE_BYTES + B_STAGE_BYTES) * (THREE ? 2 : 1);
+    static constexpr int STAGES = (196 * 1024) / STAGE_BYTES < 8 ? (196 * 1024) / STAGE_BYTES : 8;
+    static constexpr int TMEM_COLS = 2 * BLOCK_N;
+    static constexpr int THREADS = THREE ? 320 : 192;
+    static constexpr int OUT_STAGE_BYTES = BLOCK_M * 32 * 4;     // one 128 x 32 output slab
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 2 * OUT_STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+};
+
+// ------------------------------------------------------------------- kernel
+template <int BLOCK_N, bool THREE>
+__global__ void __launch_bounds__(Cfg<BLOCK_N, THREE>::THREADS, 1)
+gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
+    using C = Cfg<BLOCK_N, THREE>;
+    constexpr int STAGES = C::STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    // per stage: [A | B | (A_lo | B_lo)]
+    uint8_t *out_stage = smem + STAGES * C::STAGE_BYTES;      // 2 x [128 rows][32 floats], 128B-swizzled
+    uint64_t *bars = (uint64_t *)(out_stage + 2 * C::OUT_STAGE_BYTES);
+    uint64_t *full = bars;                    // TMA -> (splitter or MMA)
+    uint64_t *empty = bars + STAGES;          // MMA -> TMA
+    uint64_t *split = bars + 2 * STAGES;      // splitter -> MMA (three-pass only)
+    uint64_t *acc_full = bars + 3 * STAGES;   // MMA -> epilogue   [2]
+    uint64_t *acc_empty = acc_full + 2;       // epilogue -> MMA   [2]
+    uint32_t *tmem_slot = (uint32_t *)(acc_empty + 2);
+    volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int total_tiles = p.m_tiles * p.n_tiles;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+            mbar_init(&split[s], 128);
+        }
+        for (int a = 0; a < 2; a++) {
+            mbar_init(&acc_full[a], 1);
+            mbar_init(&acc_empty[a], 128);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"((uint32_t)C::TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------ TMA producer
+        if (elect_one()) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int m_tile = tile / p.n_tiles, n_tile = tile % p.n_tiles;
+                const int tw = m_tile % p.tiles_w;
+                const int th = (m_tile / p.tiles_w) % p.tiles_h;
+                const int tn = m_tile / (p.tiles_w * p.tiles_h);
+                const int w0 = tw * p.bw * p.stride - p.pad;
+                const int h0 = th * p.bh * p.stride - p.pad;
+                const int n0 = tn * p.bn;
+                for (int kb = 0; kb < p.num_k_blocks; kb++) {
+                    if (!(ok = mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status))) break;
+                    const int tap = kb / p.c_blocks, cb = kb - tap * p.c_blocks;
+                    const int kh = tap / p.ksize, kw = tap - kh * p.ksize;
+                    uint8_t *sa = smem + stage * C::STAGE_BYTES;
+                    uint8_t *sb = sa + A_STAGE_BYTES;
+                    mbar_expect_tx(&full[stage], (uint32_t)(p.tx_bytes_a + C::B_STAGE_BYTES * (THREE ? 2 : 1)));
+                    tma_load_4d(sa, &p.tm_a, &full[stage], cb * BLOCK_K, w0 + kw, h0 + kh, n0);
+                    tma_load_3d(sb, &p.tm_b, &full[stage], cb * BLOCK_K, n_tile * BLOCK_N, tap);
+                    if (THREE)
+                        tma_load_3d(sb + C::B_STAGE_BYTES + A_STAGE_BYTES, &p.tm_b_lo, &full[stage], cb * BLOCK_K,
+                                    n_tile * BLOCK_N, tap);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // -------------------------------------------------------- MMA issuer
+        if (elect_one()) {
+            constexpr uint32_t idesc = make_idesc(BLOCK_M, BLOCK_N);
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                if (!(ok = mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag, p.status))) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BLOCK_N);
+                for (int kb = 0; kb < p.num_k_blocks; kb++) {
+                    uint64_t *ready = THREE ? &split[stage] : &full[stage];
+                    if (!(ok = mbar_wait(ready, phase, abort_flag, p.status))) break;
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem + stage * C::STAGE_BYTES);
+                    const uint32_t sb = sa + A_STAGE_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BLOCK_K / UMMA_K; k++) {
+                        const uint32_t koff = k * UMMA_K * 4;
+                        const uint64_t da = make_smem_desc(sa + koff);
+                        const uint64_t db = make_smem_desc(sb + koff);
+                        if (THREE) {
+                            const uint64_t da_lo = make_smem_desc(sb + C::B_STAGE_BYTES + koff);
+                            const uint64_t db_lo = make_smem_desc(sb + C::B_STAGE_BYTES + A_STAGE_BYTES + koff);
+                            umma_tf32(d_tmem, da_lo, db, idesc, (kb | k) != 0);
+                            umma_tf32(d_tmem, da, db_lo, idesc, 1);
+                            umma_tf32(d_tmem, da, db, idesc, 1);
+                        } else {
+                            umma_tf32(d_tmem, da, db, idesc, (kb | k) != 0);
+                        }
+                    }
+                    umma_commit(&empty[stage]);     // frees the stage once these MMAs have read it
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (ok) umma_commit(&acc_full[acc]);
+                if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+            }
+        }
+        __syncwarp();
+    } else if (warp < 6) {
+        // ---------------------------------------------------------- epilogue
+        const int q = warp & 3;                 // TMEM lane quarter this warp may read
+        const int r = q * 32 + lane;            // row inside the tile
+        const int rw = r % p.bw, rh = (r / p.bw) % p.bh, rn = r / (p.bw * p.bh);
+        const bool store_thread = threadIdx.x == 64;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        int slab = 0;                           // output staging buffer in use
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            const int m_tile = tile / p.n_tiles, n_tile = tile % p.n_tiles;
+            const int tw = m_tile % p.tiles_w;
+            const int th = (m_tile / p.tiles_w) % p.tiles_h;
+            const int tn = m_tile / (p.tiles_w * p.tiles_h);
+            const int ow = tw * p.bw + rw, oh = th * p.bh + rh, n = tn * p.bn + rn;
+            const bool row_ok = (rn < p.bn) && ow < p.OW && oh < p.OH && n < p.NB;
+            const long row = ((long)n * p.OH + oh) * p.OW + ow;
+            if (!(ok = epilogue_all(mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status)))) break;
+            tc_fence_after();
+#pragma unroll 1
+            for (int chunk = 0; chunk < BLOCK_N / 32; chunk++) {
+                const int col0 = n_tile * BLOCK_N + chunk * 32;
+                if (col0 >= p.N) break;         // uniform across the CTA
+                uint32_t v[32];
+                tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BLOCK_N + chunk * 32), v);
+                tmem_ld_wait();
+                const float *arow = (p.addend && row_ok) ? p.addend + row * p.ld_addend + col0 : nullptr;
+                const bool full_cols = col0 + 32 <= p.N;
+                // affine part: folded batch-norm scale/shift + bias, optional addend
+#pragma unroll
+                for (int j = 0; j < 32; j++) {
+                    float x = __uint_as_float(v[j]);
+                    const int c = full_cols ? col0 + j : min(col0 + j, p.N - 1);
+                    if (p.scale) x *= __ldg(p.scale + c);
+                    if (p.shift) x += __ldg(p.shift + c);
+                    if (arow && (full_cols || col0 + j < p.N)) x += arow[j];
+                    v[j] = __float_as_uint(x);
+                }
+                // activation: the common ones inline, the rest through one out-of-line call per value
+                if (p.act == NB_ACT_RELU) {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) v[j] = __uint_as_float(v[j]) > 0.0f ? v[j] : 0u;
+                } else if (p.act == NB_ACT_LEAKY) {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const float x = __uint_as_float(v[j]);
+                        v[j] = __float_as_uint(x > 0.0f ? x : (float)(0.1 * (double)x));
+                    }
+                } else if (p.act != NB_ACT_LINEAR) {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) v[j] = __float_as_uint(apply_activation_call(__uint_as_float(v[j]), p.act));
+                }
+                if (p.round_out) {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) v[j] = __float_as_uint(round_tf32(__uint_as_float(v[j])));
+                }
+                if (p.tma_store) {
+                    // the store issued two slabs ago must have finished reading this buffer
+                    if (store_thread) tma_store_wait_read<1>();
+                    epilogue_bar_sync();
+                    float4 *dst = reinterpret_cast<float4 *>(out_stage + slab * C::OUT_STAGE_BYTES + r * 128);
+#pragma unroll
+                    for (int j = 0; j < 8; j++)     // 16-byte chunk j of row r lives at chunk j ^ (r % 8)
+                        dst[j ^ (r & 7)] = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                                       __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    epilogue_bar_sync();
+                    if (store_thread) {
+                        tma_store_4d(&p.tm_y, out_stage + slab * C::OUT_STAGE_BYTES, col0, tw * p.bw, th * p.bh, tn * p.bn);
+                        tma_store_commit();
+                    }
+                    slab ^= 1;
+                } else if (row_ok) {
+                    float *yrow = p.y + row * p.ldy + col0;
+#pragma unroll
+                    for (int j = 0; j < 32; j++)
+                        if (full_cols || col0 + j < p.N) yrow[j] = __uint_as_float(v[j]);
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(&acc_empty[acc]);
+            if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        }
+        if (store_thread) tma_store_wait_all();     // staged tiles must have left shared memory
+    } else if (THREE) {
+        // ---------------------------------------------- hi/lo operand splitter
+        // hi = the TF32 the tensor core would read (low 13 mantissa bits cleared),
+        // lo = x - hi (exact in fp32).  Element positions are kept, so the swizzled
+        // tile layout written by TMA is preserved.
+        const int t = threadIdx.x - 192;        // 0..127
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            for (int kb = 0; kb < p.num_k_blocks; kb++) {
+                if (!(ok = mbar_wait(&full[stage], phase, abort_flag, p.status))) break;
+                float4 *a = reinterpret_cast<float4 *>(smem + stage * C::STAGE_BYTES);
+                float4 *a_lo = reinterpret_cast<float4 *>(smem + stage * C::STAGE_BYTES + A_STAGE_BYTES + C::B_STAGE_BYTES);
+#pragma unroll
+                for (int i = 0; i < A_STAGE_BYTES / 16 / 128; i++) {
+                    float4 x = a[i * 128 + t], h, l;
+                    h.x = __uint_as_float(__float_as_uint(x.x) & 0xFFFFE000u); l.x = x.x - h.x;
+                    h.y = __uint_as_float(__float_as_uint(x.y) & 0xFFFFE000u); l.y = x.y - h.y;
+                    h.z = __uint_as_float(__float_as_uint(x.z) & 0xFFFFE000u); l.z = x.z - h.z;
+                    h.w = __uint_as_float(__float_as_uint(x.w) & 0xFFFFE000u); l.w = x.w - h.w;
+                    a[i * 128 + t] = h;
+                    a_lo[i * 128 + t] = l;
+                }
+                // make the generic-proxy writes visible to the tensor core (async proxy)
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                mbar_arrive(&split[stage]);
+                if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            }
+        }
+    }
+
+    // ------------------------------------------------------------- teardown
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        // give copies and MMAs still in flight time to land before TMEM is released
+        for (int i = 0; i < 64; i++) __nanosleep(2000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                     "r"((uint32_t)C::TMEM_COLS)
+                     : "memory");
+    }
+}
+
+// ---------------------------------------------------------------- host side
+struct Box { int bw, bh, bn; };
+
+// Chooses the (bw x bh x bn) pixel box (<= 128 rows) that wastes the fewest MMA rows.
+Box choose_box(int OW, int OH, int NB, int stride) {
+    Box best{1, 1, 1};
+    double best_eff = -1;
+    const int max_dim = 256 / std::max(1, stride);     // TMA box extent limit (elements traversed)
+    for (int bw = 1; bw <= std::min({OW, 128, max_dim}); bw++) {
+        const int rem = 128 / bw;
+        for (int bh = 1; bh <= std::min({OH, rem, max_dim}); bh++) {
+            const int bn = std::min({NB, 128 / (bw * bh), 256});
+            if (bn < 1) continue;
+            auto eff1 = [](int ext, int b) { return (double)ext / ((double)((ext + b - 1) / b) * b); };
+            double eff = eff1(OW, bw) * eff1(OH, bh) * eff1(NB, bn) * (double)(bw * bh * bn) / 128.0;
+            // prefer wider boxes on ties (longer contiguous runs per TMA request)
+            eff += 1e-6 * bw;
+            if (eff > best_eff) { best_eff = eff; best = Box{bw, bh, bn}; }
+        }
+    }
+    return best;
+}
+
+void encode(nb_handle_s *h, CUtensorMap *tm, const void *base, int rank, const cuuint64_t *dims,
+            const cuuint64_t *strides_bytes, const cuuint32_t *box, const cuuint32_t *elem_strides) {
+    CUresult r = h->encode_tiled(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, const_cast<void *>(base), dims,
+                                 strides_bytes, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) throw Error(NB_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+}
+
+template <int BLOCK_N, bool THREE>
+void launch(nb_handle_s *h, const TcParams &p) {
+    using C = Cfg<BLOCK_N, THREE>;
+    auto kern = gemm_tf32_tcgen05_kernel<BLOCK_N, THREE>;
+    static bool configured = false;
+    if (!configured) {
+        NB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+        configured = true;
+    }
+    const int tiles = p.m_tiles * p.n_tiles;
+    const int grid = std::max(1, std::min(tiles, h->sm_count));
+    kern<<<grid, C::THREADS, C::SMEM_BYTES, h->stream>>>(p);
+    check_launch("gemm_tf32_tcgen05_kernel");
+    count_launch(h);
+}
+
+inline bool aligned16(const void *p) { return ((uintptr_t)p & 15) == 0; }
+
+}  // namespace
+
+bool gemm_tc_supported(const nb_handle_s *h, const GemmArgs &a) {
+    if (!h->encode_tiled || h->cc_major != 10) return false;
+    if (a.Kc < 32 || (a.Kc % 4) != 0 || (a.ldb % 4) != 0 || !aligned16(a.b) || !aligned16(a.a)) return false;
+    if (a.a_is_conv) {
+        const ConvGeom &g = a.g;
+        // NHWC only: channel stride 1 and every other stride a multiple of 4 elements
+        if (g.sc != 1 || (g.sw % 4) || (g.sh % 4) || (g.sn % 4)) return false;
+        if (g.stride > 8) return false;
+    } else {
+        if ((a.lda % 4) != 0) return false;
+    }
+    return true;
+}
+
+void gemm_tc(nb_handle_s *h, const GemmArgs &a, bool three_pass) {
+    if (!gemm_tc_supported(h, a)) throw Error(NB_ERR_UNSUPPORTED, "operands do not satisfy the TMA layout rules");
+    if (three_pass && !a.b_lo) throw Error(NB_ERR_INVALID_ARG, "three-pass GEMM needs the low-order weight split");
+    TcParams p;
+    std::memset(&p, 0, sizeof p);
+
+    ConvGeom g;
+    if (a.a_is_conv) {
+        g = a.g;
+    } else {
+        // plain matrix = one image of height 1 and width M with Kc channels, 1x1 filter
+        g.batch = 1; g.C = a.Kc; g.H = 1; g.W = a.M; g.OH = 1; g.OW = a.M;
+        g.ksize = 1; g.stride = 1; g.pad = 0;
+        g.sc = 1; g.sw = a.lda; g.sh = (long)a.lda * a.M; g.sn = (long)a.lda * a.M;
+    }
+    const int taps = g.ksize * g.ksize;
+    Box box = choose_box(g.OW, g.OH, g.batch, g.stride);
+    p.bw = box.bw; p.bh = box.bh; p.bn = box.bn;
+    p.tiles_w = (g.OW + box.bw - 1) / box.bw;
+    p.tiles_h = (g.OH + box.bh - 1) / box.bh;
+    p.tiles_n = (g.batch + box.bn - 1) / box.bn;
+    p.OW = g.OW; p.OH = g.OH; p.NB = g.batch;
+    p.ksize = g.ksize; p.stride = g.stride; p.pad = g.pad;
+    p.c_blocks = (a.Kc + BLOCK_K - 1) / BLOCK_K;
+    p.num_k_blocks = taps * p.c_blocks;
+    p.m_tiles = p.tiles_w * p.tiles_h * p.tiles_n;
+    p.N = a.N;
+    p.tx_bytes_a = BLOCK_K * 4 * box.bw * box.bh * box.bn;
+    p.scale = a.scale; p.shift = a.shift; p.addend = a.addend; p.ld_addend = a.ld_addend;
+    p.act = a.act; p.round_out = a.round_out_tf32 ? 1 : 0;
+    p.y = a.y; p.ldy = a.ldy;
+    p.tma_store = aligned16(a.y) && (a.ldy % 4) == 0;
+    p.status = h->d_status;
+
+    // tile width in filters: widest tile that still gives every SM work
+    int block_n = 256;
+    if (three_pass) block_n = 128;
+    while (block_n > 64) {
+        const long tiles = (long)p.m_tiles * ((a.N + block_n - 1) / block_n);
+        if (a.N > block_n / 2 && tiles >= h->sm_count) break;
+        if (a.N > block_n / 2 && (long)p.m_tiles * ((a.N + block_n / 2 - 1) / (block_n / 2)) > 2L * h->sm_count) break;
+        block_n /= 2;
+    }
+    p.n_tiles = (a.N + block_n - 1) / block_n;
+
+    {   // A: dims {C, W, H, N}
+        cuuint64_t dims[4] = {(cuuint64_t)a.Kc, (cuuint64_t)g.W, (cuuint64_t)g.H, (cuuint64_t)g.batch};
+        cuuint64_t strides[3] = {(cuuint64_t)g.sw * 4, (cuuint64_t)g.sh * 4, (cuuint64_t)g.sn * 4};
+        cuuint32_t bx[4] = {(cuuint32_t)BLOCK_K, (cuuint32_t)(box.bw * g.stride), (cuuint32_t)(box.bh * g.stride),
+                            (cuuint32_t)box.bn};
+        cuuint32_t es[4] = {1, (cuuint32_t)g.stride, (cuuint32_t)g.stride, 1};
+        encode(h, &p.tm_a, a.a, 4, dims, strides, bx, es);
+    }
+    {   // B: dims {Kc, N, taps}
+        cuuint64_t dims[3] = {(cuuint64_t)a.Kc, (cuuint64_t)a.N, (cuuint64_t)taps};
+        cuuint64_t strides[2] = {(cuuint64_t)a.ldb * 4, (cuuint64_t)a.ldb * 4 * (cuuint64_t)a.N};
+        cuuint32_t bx[3] = {(cuuint32_t)BLOCK_K, (cuuint32_t)block_n, 1};
+        cuuint32_t es[3] = {1, 1, 1};
+        encode(h, &p.tm_b, a.b, 3, dims, strides, bx, es);
+        if (three_pass) encode(h, &p.tm_b_lo, a.b_lo, 3, dims, strides, bx, es);
+    }
+
+    if (p.tma_store) {   // Y: dims {N, OW, OH, NB}; the same pixel box as A, 32 columns wide
+        cuuint64_t dims[4] = {(cuuint64_t)a.N, (cuuint64_t)g.OW, (cuuint64_t)g.OH, (cuuint64_t)g.batch};
+        cuuint64_t strides[3] = {(cuuint64_t)a.ldy * 4, (cuuint64_t)a.ldy * 4 * (cuuint64_t)g.OW,
+                                 (cuuint64_t)a.ldy * 4 * (cuuint64_t)g.OW * (cuuint64_t)g.OH};
+        cuuint32_t bx[4] = {32, (cuuint32_t)box.bw, (cuuint32_t)box.bh, (cuuint32_t)box.bn};
+        cuuint32_t es[4] = {1, 1, 1, 1};
+        encode(h, &p.tm_y, a.y, 4, dims, strides, bx, es);
+    }
+
+    ProfileScope prof(h, 0, 2.0 * (double)a.M * a.N * a.Kc * taps);
+    if (three_pass) {
+        if (block_n == 128) launch<128, true>(h, p);
+        else launch<64, true>(h, p);
+    } else {
+        if (block_n == 256) launch<256, false>(h, p);
+        else if (block_n == 128) launch<128, false>(h, p);
+        else launch<64, false>(h, p);
+    }
+}
+
+}  // namespace nb

@@ -1,0 +1,177 @@
+// Internal declarations shared by the kernels and the C-ABI layer.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "../../include/nebula_b200.h"
+
+namespace nb {
+
+// ----------------------------------------------------------------- errors
+struct Error : std::runtime_error {
+    int code;
+    Error(int c, const std::string &m) : std::runtime_error(m), code(c) {}
+};
+
+#define NB_CHECK_CUDA(expr)                                                                     \
+    do {                                                                                        \
+        cudaError_t _e = (expr);                                                                \
+        if (_e != cudaSuccess)                                                                  \
+            throw nb::Error(NB_ERR_CUDA, std::string(#expr) + ": " + cudaGetErrorString(_e));   \
+    } while (0)
+
+#define NB_REQUIRE(cond, msg)                                                  \
+    do {                                                                       \
+        if (!(cond)) throw nb::Error(NB_ERR_INVALID_ARG, std::string(msg));    \
+    } while (0)
+
+// device status word written by kernels whose bounded waits give up
+enum : int { DEV_OK = 0, DEV_TIMEOUT = 1 };
+
+}  // namespace nb
+
+typedef CUresult (*nb_encode_tiled_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                       const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                                       CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                       CUtensorMapFloatOOBfill);
+
+struct nb_handle_s {
+    int device = 0;
+    cudaStream_t stream = 0;
+    int math_mode = NB_MATH_TF32;
+    int sm_count = 0;
+    int cc_major = 0;
+    std::string last_error;
+    int *d_status = nullptr;            // device status word (nb::DEV_*)
+    nb_encode_tiled_fn encode_tiled = nullptr;
+    unsigned long long launches = 0;
+    // optional per-launch event timing of the contraction kernels
+    struct Timed { cudaEvent_t start, stop; double flops; int kind; };
+    bool profiling = false;
+    std::vector<Timed> timed;
+};
+
+namespace nb {
+
+// ------------------------------------------------------------ device memory
+struct DeviceBuffer {
+    float *p = nullptr;
+    size_t n = 0;
+    DeviceBuffer() {}
+    DeviceBuffer(const DeviceBuffer &) = delete;
+    DeviceBuffer &operator=(const DeviceBuffer &) = delete;
+    ~DeviceBuffer() { release(); }
+    void alloc(size_t count) {
+        release();
+        if (count) NB_CHECK_CUDA(cudaMalloc((void **)&p, count * sizeof(float)));
+        n = count;
+    }
+    void release() {
+        if (p) cudaFree(p);
+        p = nullptr;
+        n = 0;
+    }
+};
+
+// -------------------------------------------------------------- GEMM core
+// D[M,N] = A[M,K] * B[N,K]^T, both operands K-major, with a fused epilogue
+//   v = acc * scale[n] + shift[n] (+ addend[m,n]);  y[m,n] = act(v)
+// A is either a plain row-major matrix or an implicit im2col view of an NHWC
+// (or arbitrarily strided) activation tensor: row m = (image, oh, ow), column
+// k = (kh, kw, c) with c fastest.
+struct ConvGeom {
+    int batch = 1, C = 1, H = 1, W = 1;     // input extents
+    int OH = 1, OW = 1;                     // output extents
+    int ksize = 1, stride = 1, pad = 0;
+    // element strides of the input tensor (for the CUDA-core gather path)
+    long sn = 0, sc = 1, sh = 0, sw = 0;
+};
+
+struct GemmArgs {
+    // A operand
+    const float *a = nullptr;
+    bool a_is_conv = false;     // false: plain [M,K] with row stride lda
+    long lda = 0;
+    ConvGeom g;                 // used when a_is_conv
+    // B operand: [taps][N][Kc] (taps = ksize*ksize, Kc = channels per tap, row stride ldb)
+    const float *b = nullptr;       // operand used by the TF32 / FP32 paths
+    const float *b_lo = nullptr;    // low-order split of B for the 3xTF32 path
+    long ldb = 0;
+    int M = 0, N = 0;           // logical output extents
+    int Kc = 0;                 // contraction length per tap (channels or FC inputs)
+    // epilogue
+    const float *scale = nullptr;   // may be null (=1)
+    const float *shift = nullptr;   // may be null (=0)
+    const float *addend = nullptr;  // may be null; same indexing as y
+    long ld_addend = 0;
+    int act = NB_ACT_LINEAR;
+    bool round_out_tf32 = false;    // store RN(TF32) values (the consumer is a TF32 contraction)
+    float *y = nullptr;
+    long ldy = 0;
+};
+
+// Tensor-core path (tcgen05 + TMA).  Throws nb::Error(NB_ERR_UNSUPPORTED) when the
+// operands do not meet TMA's layout rules; callers then use gemm_simt.
+bool gemm_tc_supported(const nb_handle_s *h, const GemmArgs &a);
+void gemm_tc(nb_handle_s *h, const GemmArgs &a, bool three_pass);
+// CUDA-core fp32 path: any extents, strides and alignments.
+void gemm_simt(nb_handle_s *h, const GemmArgs &a);
+// Dispatch on the handle's math mode.
+void gemm(nb_handle_s *h, const GemmArgs &a);
+
+// ------------------------------------------------------- elementwise et al.
+void launch_activation(nb_handle_s *h, int act, float *data, size_t n);
+void launch_bias(nb_handle_s *h, float *out, const float *bias, unsigned channel, unsigned size, unsigned batch);
+void launch_bn_normalize(nb_handle_s *h, float *out, const float *mean, const float *var, unsigned channel,
+                         unsigned size, unsigned batch);
+void launch_bn_scale(nb_handle_s *h, float *out, const float *scale, unsigned channel, unsigned size,
+                     unsigned batch);
+void launch_softmax(nb_handle_s *h, const float *x, float *y, int rows, int classes);
+// src NCHW -> dst NHWC (to_nhwc) or back; optional TF32 rounding of the copy
+void launch_layout(nb_handle_s *h, const float *src, float *dst, int B, int C, int H, int W, bool to_nhwc,
+                   bool round_tf32);
+void launch_round_tf32(nb_handle_s *h, const float *src, float *dst, size_t n);
+void launch_split_tf32(nb_handle_s *h, const float *src, float *hi, float *lo, size_t n);
+void launch_pool(nb_handle_s *h, const nb_pool_desc_t &d, const float *x, float *y, bool round_tf32);
+void launch_shortcut(nb_handle_s *h, const nb_shortcut_desc_t &d, const float *prev, const float *conn, float *y,
+                     bool round_tf32);
+// weights OIHW [F,C,k,k] -> [k*k][F][Cp] (Cp >= C, zero padded), optionally permuting FC columns
+void launch_weight_relayout(nb_handle_s *h, const float *w_oihw, float *dst, int F, int C, int k, int Cp);
+// FC weights whose columns index (c,h,w) -> columns indexing (h,w,c)
+void launch_fc_permute(nb_handle_s *h, const float *w, float *dst, int out, int C, int H, int W);
+// LSTM cell: z [B,4H] (gate blocks i,f,g,o) -> c_t, h_t (+ TF32-rounded copy of h_t)
+void launch_lstm_cell(nb_handle_s *h, const float *z, const float *c_prev, float *c_out, float *h_out,
+                      float *h_round, int B, int H);
+
+// _gemm_ of the operator library: row-major C = alpha*op(A)*op(B) + beta*C
+void launch_sgemm(nb_handle_s *h, bool ta, bool tb, int M, int N, int K, float alpha, const float *A, int lda,
+                  const float *B, int ldb, float beta, float *C, int ldc);
+
+// Brackets one contraction launch with events while profiling is on (kind 0 = tensor-core, 1 = CUDA-core).
+struct ProfileScope {
+    nb_handle_s *h;
+    nb_handle_s::Timed t;
+    bool on;
+    ProfileScope(nb_handle_s *hh, int kind, double flops) : h(hh), on(hh->profiling) {
+        if (!on) return;
+        t.kind = kind; t.flops = flops;
+        cudaEventCreate(&t.start); cudaEventCreate(&t.stop);
+        cudaEventRecord(t.start, h->stream);
+    }
+    ~ProfileScope() {
+        if (!on) return;
+        cudaEventRecord(t.stop, h->stream);
+        h->timed.push_back(t);
+    }
+};
+
+inline void count_launch(nb_handle_s *h, int n = 1) { h->launches += (unsigned long long)n; }
+void check_launch(const char *what);
+
+}  // namespace nb

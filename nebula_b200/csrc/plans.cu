@@ -1,0 +1,356 @@
+// Per-layer plans: weight upload/re-layout and the forward bodies that a Nebula
+// layer's _forward_() would call.
+#include "plans.h"
+
+#include <cmath>
+#include <cstring>
+
+namespace nb {
+
+void upload(nb_handle_s *h, DeviceBuffer &dst, const float *src, size_t n, int mem) {
+    dst.alloc(n);
+    if (!n) return;
+    NB_REQUIRE(src != nullptr, "null source pointer");
+    NB_CHECK_CUDA(cudaMemcpyAsync(dst.p, src, n * sizeof(float),
+                                  mem == NB_MEM_DEVICE ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, h->stream));
+    if (mem == NB_MEM_HOST) NB_CHECK_CUDA(cudaStreamSynchronize(h->stream));   // the host buffer may go away
+}
+void upload_vec(nb_handle_s *h, DeviceBuffer &dst, const std::vector<float> &v) {
+    upload(h, dst, v.data(), v.size(), NB_MEM_HOST);
+}
+std::vector<float> to_host(nb_handle_s *h, const float *src, size_t n, int mem) {
+    std::vector<float> v(n);
+    if (!n) return v;
+    NB_REQUIRE(src != nullptr, "null source pointer");
+    if (mem == NB_MEM_DEVICE) {
+        NB_CHECK_CUDA(cudaMemcpyAsync(v.data(), src, n * sizeof(float), cudaMemcpyDeviceToHost, h->stream));
+        NB_CHECK_CUDA(cudaStreamSynchronize(h->stream));
+    } else {
+        std::memcpy(v.data(), src, n * sizeof(float));
+    }
+    return v;
+}
+
+void fold_bn(int n, const float *bias, const float *gamma, const float *mean, const float *var, bool has_bn,
+             std::vector<float> &scale, std::vector<float> &shift) {
+    scale.clear();
+    shift.resize(n);
+    if (!has_bn) {
+        for (int i = 0; i < n; i++) shift[i] = bias[i];
+        return;
+    }
+    scale.resize(n);
+    for (int i = 0; i < n; i++) {
+        const double s = (double)gamma[i] / (std::sqrt((double)var[i]) + 0.00001);
+        scale[i] = (float)s;
+        shift[i] = (float)((double)bias[i] - (double)mean[i] * s);
+    }
+}
+
+// -------------------------------------------------------------------- conv
+ConvPlan::ConvPlan(nb_handle_s *hh, const nb_conv2d_desc_t &desc) : nb_plan_s(NB_PLAN_CONV, hh), d(desc) {
+    NB_REQUIRE(d.batch > 0 && d.channels > 0 && d.height > 0 && d.width > 0, "conv: non-positive input extent");
+    NB_REQUIRE(d.filters > 0 && d.size > 0 && d.stride > 0 && d.padding >= 0, "conv: bad filter geometry");
+    NB_REQUIRE(d.height + 2 * d.padding >= d.size && d.width + 2 * d.padding >= d.size, "conv: filter larger than padded input");
+    NB_REQUIRE(d.activation > NB_ACT_UNDEFINED && d.activation < NB_ACT_COUNT, "conv: undefined activation");
+    NB_REQUIRE(d.layout == NB_LAYOUT_NCHW || d.layout == NB_LAYOUT_NHWC, "conv: bad layout");
+    // convolutional_layer.cc:150-151
+    OH = (d.height + 2 * d.padding - d.size) / d.stride + 1;
+    OW = (d.width + 2 * d.padding - d.size) / d.stride + 1;
+    Cp = (d.channels + 3) / 4 * 4;
+}
+
+void ConvPlan::set_weights(const float *weight, const float *bias, const float *g, const float *m, const float *v,
+                           int mem) {
+    NB_REQUIRE(weight && bias, "conv: null weight or bias");
+    NB_REQUIRE(!d.batch_normalize || (g && m && v), "conv: batch_normalize=1 needs scale, mean and variance");
+    const size_t wn = (size_t)d.filters * d.channels * d.size * d.size;
+    DeviceBuffer raw;
+    upload(h, raw, weight, wn, mem);
+    w.exact.alloc((size_t)d.size * d.size * d.filters * Cp);
+    w.split_ready = false;
+    launch_weight_relayout(h, raw.p, w.exact.p, d.filters, d.channels, d.size, Cp);
+    NB_CHECK_CUDA(cudaStreamSynchronize(h->stream));
+    std::vector<float> hb = to_host(h, bias, d.filters, mem), hg, hm, hv, sc, sh;
+    if (d.batch_normalize) {
+        hg = to_host(h, g, d.filters, mem);
+        hm = to_host(h, m, d.filters, mem);
+        hv = to_host(h, v, d.filters, mem);
+    }
+    fold_bn(d.filters, hb.data(), hg.data(), hm.data(), hv.data(), d.batch_normalize != 0, sc, sh);
+    has_scale = !sc.empty();
+    if (has_scale) upload_vec(h, scale, sc);
+    upload_vec(h, shift, sh);
+    ready = true;
+}
+
+GemmPath ConvPlan::path(const ForwardOpts &) const {
+    if (h->math_mode == NB_MATH_FP32) return PATH_SIMT;
+    const bool tc_ok = h->encode_tiled && h->cc_major == 10 && Cp == d.channels && d.channels >= 32 && d.stride <= 8;
+    if (!tc_ok) return PATH_SIMT;
+    return h->math_mode == NB_MATH_TF32X3 ? PATH_TC3 : PATH_TC;
+}
+
+void ConvPlan::forward(const float *x, float *y, const ForwardOpts &o) {
+    if (!ready) throw Error(NB_ERR_NO_WEIGHTS, "conv: forward before set_weights");
+    NB_REQUIRE(x && y, "conv: null tensor pointer");
+    const GemmPath pth = path(o);
+    const size_t xin = (size_t)d.batch * d.channels * d.height * d.width;
+    const size_t yout = (size_t)d.batch * d.filters * OH * OW;
+
+    GemmArgs a;
+    a.a_is_conv = true;
+    ConvGeom &g = a.g;
+    g.batch = d.batch; g.C = d.channels; g.H = d.height; g.W = d.width; g.OH = OH; g.OW = OW;
+    g.ksize = d.size; g.stride = d.stride; g.pad = d.padding;
+
+    const float *xa = x;
+    bool nhwc = o.x_nhwc;
+    if (pth != PATH_SIMT) {
+        const bool need_round = (pth == PATH_TC) && !o.x_rounded;
+        if (!nhwc) {
+            if (x_scratch.n < xin) x_scratch.alloc(xin);
+            launch_layout(h, x, x_scratch.p, d.batch, d.channels, d.height, d.width, true, need_round);
+            xa = x_scratch.p;
+            nhwc = true;
+        } else if (need_round) {
+            if (x_scratch.n < xin) x_scratch.alloc(xin);
+            launch_round_tf32(h, x, x_scratch.p, xin);
+            xa = x_scratch.p;
+        }
+    }
+    if (nhwc) {
+        g.sc = 1; g.sw = d.channels; g.sh = (long)d.width * d.channels; g.sn = (long)d.height * d.width * d.channels;
+    } else {
+        g.sw = 1; g.sh = d.width; g.sc = (long)d.height * d.width; g.sn = (long)d.channels * d.height * d.width;
+    }
+    a.a = xa;
+    a.ldb = Cp;
+    a.M = d.batch * OH * OW;
+    a.N = d.filters;
+    a.Kc = d.channels;
+    a.scale = has_scale ? scale.p : nullptr;
+    a.shift = shift.p;
+    a.act = d.activation;
+    a.round_out_tf32 = o.round_out;
+    a.addend = o.addend;
+    a.ld_addend = d.filters;
+    float *yo = y;
+    if (!o.y_nhwc) {
+        NB_REQUIRE(o.addend == nullptr, "conv: addend needs NHWC output");
+        if (y_scratch.n < yout) y_scratch.alloc(yout);
+        yo = y_scratch.p;
+    }
+    a.y = yo;
+    a.ldy = d.filters;
+    if (pth == PATH_SIMT) {
+        a.b = w.exact.p;
+        gemm_simt(h, a);
+    } else {
+        w.ensure_split(h);
+        a.b = w.hi.p;
+        a.b_lo = w.lo.p;
+        gemm_tc(h, a, pth == PATH_TC3);
+    }
+    if (!o.y_nhwc) launch_layout(h, yo, y, d.batch, d.filters, OH, OW, false, false);
+}
+
+// ---------------------------------------------------------------------- fc
+FcPlan::FcPlan(nb_handle_s *hh, const nb_fc_desc_t &desc) : nb_plan_s(NB_PLAN_FC, hh), d(desc) {
+    NB_REQUIRE(d.batch > 0 && d.inputs > 0 && d.outputs > 0, "connected: non-positive extent");
+    NB_REQUIRE(d.activation > NB_ACT_UNDEFINED && d.activation < NB_ACT_COUNT, "connected: undefined activation");
+}
+
+void FcPlan::set_weights(const float *weight, const float *bias, const float *g, const float *m, const float *v,
+                         int mem) {
+    NB_REQUIRE(weight && bias, "connected: null weight or bias");
+    NB_REQUIRE(!d.batch_normalize || (g && m && v), "connected: batch_normalize=1 needs scale, mean and variance");
+    const size_t wn = (size_t)d.outputs * d.inputs;
+    w.split_ready = false;
+    if (perm_c > 0 && perm_h * perm_w > 1) {
+        NB_REQUIRE((size_t)perm_c * perm_h * perm_w == (size_t)d.inputs, "connected: permutation does not match inputs");
+        DeviceBuffer raw;
+        upload(h, raw, weight, wn, mem);
+        w.exact.alloc(wn);
+        launch_fc_permute(h, raw.p, w.exact.p, d.outputs, perm_c, perm_h, perm_w);
+        NB_CHECK_CUDA(cudaStreamSynchronize(h->stream));
+    } else {
+        upload(h, w.exact, weight, wn, mem);
+    }
+    std::vector<float> hb = to_host(h, bias, d.outputs, mem), hg, hm, hv, sc, sh;
+    if (d.batch_normalize) {
+        hg = to_host(h, g, d.outputs, mem);
+        hm = to_host(h, m, d.outputs, mem);
+        hv = to_host(h, v, d.outputs, mem);
+    }
+    fold_bn(d.outputs, hb.data(), hg.data(), hm.data(), hv.data(), d.batch_normalize != 0, sc, sh);
+    has_scale = !sc.empty();
+    if (has_scale) upload_vec(h, scale, sc);
+    upload_vec(h, shift, sh);
+    ready = true;
+}
+
+GemmPath FcPlan::path() const {
+    if (h->math_mode == NB_MATH_FP32) return PATH_SIMT;
+    const bool tc_ok = h->encode_tiled && h->cc_major == 10 && (d.inputs % 4) == 0 && d.inputs >= 32;
+    if (!tc_ok) return PATH_SIMT;
+    return h->math_mode == NB_MATH_TF32X3 ? PATH_TC3 : PATH_TC;
+}
+
+void FcPlan::forward(const float *x, float *y, const ForwardOpts &o, int rows) {
+    if (!ready) throw Error(NB_ERR_NO_WEIGHTS, "connected: forward before set_weights");
+    NB_REQUIRE(x && y, "connected: null tensor pointer");
+    const int M = rows > 0 ? rows : d.batch;
+    GemmPath pth = path();
+    if (pth != PATH_SIMT && (((uintptr_t)x) & 15)) pth = PATH_SIMT;
+    GemmArgs a;
+    const float *xa = x;
+    if (pth == PATH_TC && !o.x_rounded) {
+        const size_t n = (size_t)M * d.inputs;
+        if (x_scratch.n < n) x_scratch.alloc(n);
+        launch_round_tf32(h, x, x_scratch.p, n);
+        xa = x_scratch.p;
+    }
+    a.a = xa; a.lda = d.inputs;
+    a.ldb = d.inputs;
+    a.M = M; a.N = d.outputs; a.Kc = d.inputs;
+    a.scale = has_scale ? scale.p : nullptr;
+    a.shift = shift.p;
+    a.act = d.activation;
+    a.round_out_tf32 = o.round_out;
+    a.addend = o.addend; a.ld_addend = d.outputs;
+    a.y = y; a.ldy = d.outputs;
+    if (pth == PATH_SIMT) {
+        a.b = w.exact.p;
+        gemm_simt(h, a);
+    } else {
+        w.ensure_split(h);
+        a.b = w.hi.p; a.b_lo = w.lo.p;
+        gemm_tc(h, a, pth == PATH_TC3);
+    }
+}
+
+// -------------------------------------------------------------------- lstm
+LstmPlan::LstmPlan(nb_handle_s *hh, const nb_lstm_desc_t &desc) : nb_plan_s(NB_PLAN_LSTM, hh), d(desc) {
+    NB_REQUIRE(d.time_steps > 0 && d.batch > 0 && d.inputs > 0 && d.hidden > 0, "lstm: non-positive extent");
+    if (d.activation != NB_ACT_LINEAR)
+        throw Error(NB_ERR_UNSUPPORTED, "lstm: only activation=linear gate layers are supported");
+}
+
+size_t LstmPlan::weight_count() const {
+    size_t n = 0;
+    for (int gidx = 0; gidx < 8; gidx++) {
+        const size_t gin = gidx < 4 ? d.hidden : d.inputs;
+        n += (size_t)d.hidden + (size_t)d.hidden * gin + (d.batch_normalize ? 3 * (size_t)d.hidden : 0);
+    }
+    return n;
+}
+
+void LstmPlan::set_weights(const float *stream, size_t count, int mem) {
+    if (count != weight_count())
+        throw Error(NB_ERR_WEIGHTS, "lstm: weight stream has " + std::to_string(count) + " floats, layer needs " +
+                                        std::to_string(weight_count()));
+    std::vector<float> hs = to_host(h, stream, count, mem);
+    const int H = d.hidden, in = d.inputs;
+    struct Blob { const float *bias, *w, *g, *m, *v; };
+    Blob blob[8];
+    size_t pos = 0;
+    for (int gidx = 0; gidx < 8; gidx++) {     // file order iW,fW,oW,cW,iU,fU,oU,cU (lstm_layer.cc:194-206)
+        const size_t gin = gidx < 4 ? H : in;
+        blob[gidx].bias = hs.data() + pos; pos += H;
+        blob[gidx].w = hs.data() + pos; pos += (size_t)H * gin;
+        blob[gidx].g = blob[gidx].m = blob[gidx].v = nullptr;
+        if (d.batch_normalize) {
+            blob[gidx].g = hs.data() + pos; pos += H;
+            blob[gidx].m = hs.data() + pos; pos += H;
+            blob[gidx].v = hs.data() + pos; pos += H;
+        }
+    }
+    // gate rows in the order i, f, g(cell), o; file indices of those gates:
+    const int file_of_gate[4] = {0, 1, 3, 2};
+    std::vector<float> u((size_t)4 * H * in), wr((size_t)4 * H * H), sh((size_t)4 * H, 0.0f);
+    for (int gate = 0; gate < 4; gate++) {
+        for (int side = 0; side < 2; side++) {      // 0: W (recurrent), 1: U (input)
+            const Blob &b = blob[file_of_gate[gate] + (side ? 4 : 0)];
+            const size_t gin = side ? in : H;
+            std::vector<float> sc, s1;
+            fold_bn(H, b.bias, b.g, b.m, b.v, d.batch_normalize != 0, sc, s1);
+            float *dst = (side ? u.data() : wr.data()) + (size_t)gate * H * gin;
+            for (int r = 0; r < H; r++) {
+                const float s = sc.empty() ? 1.0f : sc[r];
+                for (size_t c = 0; c < gin; c++) dst[(size_t)r * gin + c] = b.w[(size_t)r * gin + c] * s;
+                sh[(size_t)gate * H + r] += s1[r];
+            }
+        }
+    }
+    upload_vec(h, wu.exact, u);
+    upload_vec(h, ww.exact, wr);
+    wu.split_ready = ww.split_ready = false;
+    upload_vec(h, shift, sh);
+    ready = true;
+}
+
+void LstmPlan::forward(const float *x, float *out, float *cell, bool x_rounded, float *out_round) {
+    if (!ready) throw Error(NB_ERR_NO_WEIGHTS, "lstm: forward before set_weights");
+    NB_REQUIRE(x && out, "lstm: null tensor pointer");
+    const int T = d.time_steps, B = d.batch, H = d.hidden, in = d.inputs;
+    const size_t rows = (size_t)T * B;
+    const bool tc_u = h->math_mode != NB_MATH_FP32 && h->encode_tiled && h->cc_major == 10 && (in % 4) == 0 && in >= 32 &&
+                      !(((uintptr_t)x) & 15);
+    const bool tc_w = h->math_mode != NB_MATH_FP32 && h->encode_tiled && h->cc_major == 10 && (H % 4) == 0 && H >= 32;
+    const bool three = h->math_mode == NB_MATH_TF32X3;
+    if (pre.n < rows * 4 * H) pre.alloc(rows * 4 * H);
+    if (z.n < (size_t)B * 4 * H) z.alloc((size_t)B * 4 * H);
+    if (!cell) {
+        if (cell_own.n < rows * H) cell_own.alloc(rows * H);
+        cell = cell_own.p;
+    }
+    float *hr = out_round;
+    if (!hr && tc_w && !three) {
+        if (h_round.n < rows * H) h_round.alloc(rows * H);
+        hr = h_round.p;
+    }
+    // 1. input-side projection of every time step in one GEMM: pre = X * U^T + (bU + bW)
+    {
+        const float *xa = x;
+        if (tc_u && !three && !x_rounded) {
+            if (x_round.n < rows * in) x_round.alloc(rows * in);
+            launch_round_tf32(h, x, x_round.p, rows * in);
+            xa = x_round.p;
+        }
+        GemmArgs a;
+        a.a = xa; a.lda = in; a.ldb = in; a.M = (int)rows; a.N = 4 * H; a.Kc = in;
+        a.shift = shift.p; a.act = NB_ACT_LINEAR; a.y = pre.p; a.ldy = 4 * H;
+        if (tc_u) {
+            wu.ensure_split(h);
+            a.b = wu.hi.p; a.b_lo = wu.lo.p;
+            gemm_tc(h, a, three);
+        } else {
+            a.b = wu.exact.p;
+            gemm_simt(h, a);
+        }
+    }
+    // 2. the recurrence: z_t = pre_t + h_{t-1} * W^T, then the cell update
+    for (int t = 0; t < T; t++) {
+        const float *zt = pre.p + (size_t)t * B * 4 * H;
+        if (t > 0) {
+            GemmArgs a;
+            const float *hprev = (tc_w && !three) ? hr + (size_t)(t - 1) * B * H : out + (size_t)(t - 1) * B * H;
+            a.a = hprev; a.lda = H; a.ldb = H; a.M = B; a.N = 4 * H; a.Kc = H;
+            a.addend = zt; a.ld_addend = 4 * H; a.act = NB_ACT_LINEAR; a.y = z.p; a.ldy = 4 * H;
+            if (tc_w) {
+                ww.ensure_split(h);
+                a.b = ww.hi.p; a.b_lo = ww.lo.p;
+                gemm_tc(h, a, three);
+            } else {
+                a.b = ww.exact.p;
+                gemm_simt(h, a);
+            }
+            zt = z.p;
+        }
+        launch_lstm_cell(h, zt, t ? cell + (size_t)(t - 1) * B * H : nullptr, cell + (size_t)t * B * H,
+                         out + (size_t)t * B * H, hr ? hr + (size_t)t * B * H : nullptr, B, H);
+    }
+}
+
+}  // namespace nb

@@ -1,0 +1,104 @@
+// Plan objects behind the C ABI: per-layer state that a Nebula layer would own
+// (re-laid-out weights, folded batch-norm vectors, scratch for layout changes).
+#pragma once
+
+#include <memory>
+
+#include "nb_internal.h"
+
+enum nb_plan_kind { NB_PLAN_CONV = 1, NB_PLAN_FC = 2, NB_PLAN_LSTM = 3 };
+
+struct nb_plan_s {
+    int kind;
+    nb_handle_s *h;
+    nb_plan_s(int k, nb_handle_s *hh) : kind(k), h(hh) {}
+    virtual ~nb_plan_s() {}
+    virtual void output_dims(int dims[3]) const = 0;
+};
+
+namespace nb {
+
+enum GemmPath { PATH_TC = 0, PATH_TC3 = 1, PATH_SIMT = 2 };
+
+// Weights of one contraction in the three forms the math modes need.
+struct WeightSet {
+    DeviceBuffer exact;     // fp32 as loaded (re-laid out)
+    DeviceBuffer hi, lo;    // TF32 split, built on first use
+    bool split_ready = false;
+    void ensure_split(nb_handle_s *h) {
+        if (split_ready) return;
+        hi.alloc(exact.n);
+        lo.alloc(exact.n);
+        launch_split_tf32(h, exact.p, hi.p, lo.p, exact.n);
+        split_ready = true;
+    }
+};
+
+// Folds the reference's inference batch-norm + bias into y = acc*scale + shift:
+// (acc - mean) / (sqrt(var) + 1e-5) * gamma + bias  (common/batchnorm.cc:58-97,
+// common/utils.cc:162-179).  Without batch-norm scale is absent and shift = bias.
+void fold_bn(int n, const float *bias, const float *gamma, const float *mean, const float *var, bool has_bn,
+             std::vector<float> &scale, std::vector<float> &shift);
+
+struct ForwardOpts {
+    bool x_nhwc = false;            // conv: x already NHWC (else NCHW, the reference layout)
+    bool y_nhwc = false;            // conv: write y as NHWC
+    bool x_rounded = false;         // x already holds TF32-rounded values
+    bool round_out = false;         // store TF32-rounded outputs (consumer is a TF32 contraction)
+    const float *addend = nullptr;  // optional tensor added before the activation (same layout as y)
+};
+
+struct ConvPlan : nb_plan_s {
+    nb_conv2d_desc_t d;
+    int OH, OW, Cp;
+    WeightSet w;                    // [tap][F][Cp]
+    DeviceBuffer scale, shift;
+    bool has_scale = false, ready = false;
+    DeviceBuffer x_scratch, y_scratch;
+    ConvPlan(nb_handle_s *h, const nb_conv2d_desc_t &desc);
+    void set_weights(const float *weight, const float *bias, const float *g, const float *m, const float *v, int mem);
+    void forward(const float *x, float *y, const ForwardOpts &o);
+    void output_dims(int dims[3]) const override { dims[0] = d.filters; dims[1] = OH; dims[2] = OW; }
+    GemmPath path(const ForwardOpts &o) const;
+};
+
+struct FcPlan : nb_plan_s {
+    nb_fc_desc_t d;
+    WeightSet w;                    // [out][in]
+    DeviceBuffer scale, shift;
+    bool has_scale = false, ready = false;
+    DeviceBuffer x_scratch;
+    // when the input is an NHWC activation, columns are permuted (c,h,w) -> (h,w,c)
+    int perm_c = 0, perm_h = 0, perm_w = 0;
+    FcPlan(nb_handle_s *h, const nb_fc_desc_t &desc);
+    void set_weights(const float *weight, const float *bias, const float *g, const float *m, const float *v, int mem);
+    void forward(const float *x, float *y, const ForwardOpts &o, int rows = -1);
+    void output_dims(int dims[3]) const override { dims[0] = d.outputs; dims[1] = 1; dims[2] = 1; }
+    GemmPath path() const;
+};
+
+struct LstmPlan : nb_plan_s {
+    nb_lstm_desc_t d;
+    WeightSet wu;                   // [4H][in]  input-side gates, rows i,f,g,o
+    WeightSet ww;                   // [4H][H]   recurrent gates
+    DeviceBuffer shift;             // [4H] summed biases (+ folded batch-norm shifts)
+    DeviceBuffer pre;               // [T*B][4H] input-side projection for all steps
+    DeviceBuffer z;                 // [B][4H]   gate pre-activations of one step
+    DeviceBuffer cell_own;          // [T*B][H]  when the caller passes no cell buffer
+    DeviceBuffer h_round;           // [T*B][H]  TF32-rounded hidden states
+    DeviceBuffer x_round;           // [T*B][in]
+    bool ready = false;
+    LstmPlan(nb_handle_s *h, const nb_lstm_desc_t &desc);
+    void set_weights(const float *stream, size_t count, int mem);
+    size_t weight_count() const;
+    // out_round (optional): receives a TF32-rounded copy of out
+    void forward(const float *x, float *out, float *cell, bool x_rounded, float *out_round);
+    void output_dims(int dims[3]) const override { dims[0] = d.hidden; dims[1] = 1; dims[2] = 1; }
+};
+
+// host or device source -> freshly filled device buffer
+void upload(nb_handle_s *h, DeviceBuffer &dst, const float *src, size_t n, int mem);
+void upload_vec(nb_handle_s *h, DeviceBuffer &dst, const std::vector<float> &v);
+std::vector<float> to_host(nb_handle_s *h, const float *src, size_t n, int mem);
+
+}  // namespace nb

@@ -1,0 +1,107 @@
+"""Single-layer micro-benchmark through the C ABI (device-resident NHWC tensors).
+
+    python -m nebula_b200.microbench conv --batch 64 --channels 256 --size 56 --filters 256 --k 3 --pad 1
+    python -m nebula_b200.microbench fc --batch 256 --inputs 25088 --outputs 4096
+    python -m nebula_b200.microbench sweep        # the single-convolution sweep (batch 64, stride 1)
+
+Prints one JSON line per case: device time per call (CUDA events on the stream
+the kernels run on), algorithmic TFLOP/s and GB/s.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+from . import api
+
+
+def _time(fn, iters, warmup):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def bench_conv(h, batch, channels, size, filters, k, stride, pad, math, iters=10, warmup=3, bn=False, act="relu"):
+    h.set_math(math)
+    plan = api.Conv2d(h, batch, channels, size, size, filters, k, stride, pad, bn, act, api.LAYOUT_NHWC)
+    g = torch.Generator(device="cuda").manual_seed(1)
+    w = torch.randn(filters, channels, k, k, device="cuda", generator=g) * (2.0 / (channels * k * k)) ** 0.5
+    b = torch.zeros(filters, device="cuda")
+    bnp = (torch.ones(filters, device="cuda"), torch.zeros(filters, device="cuda"), torch.ones(filters, device="cuda"))
+    plan.set_weights(w, b, bnp if bn else None)
+    x = torch.randn(batch, size, size, channels, device="cuda", generator=g)
+    c, oh, ow = plan.output_dims()
+    y = torch.empty(batch, oh, ow, c, device="cuda")
+    fwd = lambda: h.check(h.lib.nb_conv2d_forward(plan.p, x.data_ptr(), y.data_ptr()))
+    ms = _time(fwd, iters, warmup)
+    h.synchronize()
+    flops = 2.0 * batch * filters * oh * ow * channels * k * k
+    nbytes = 4.0 * (x.numel() + y.numel() + w.numel())
+    plan.close()
+    return dict(op="conv", batch=batch, channels=channels, size=size, filters=filters, k=k, stride=stride, pad=pad,
+                math=math, ms=round(ms, 4), tflops=round(flops / ms / 1e9, 1), gbs=round(nbytes / ms / 1e6, 1))
+
+
+def bench_fc(h, batch, inputs, outputs, math, iters=10, warmup=3):
+    h.set_math(math)
+    plan = api.Connected(h, batch, inputs, outputs, False, "relu")
+    g = torch.Generator(device="cuda").manual_seed(2)
+    plan.set_weights(torch.randn(outputs, inputs, device="cuda", generator=g) * (1.0 / inputs) ** 0.5,
+                     torch.zeros(outputs, device="cuda"))
+    x = torch.randn(batch, inputs, device="cuda", generator=g)
+    y = torch.empty(batch, outputs, device="cuda")
+    fwd = lambda: h.check(h.lib.nb_fc_forward(plan.p, x.data_ptr(), y.data_ptr()))
+    ms = _time(fwd, iters, warmup)
+    h.synchronize()
+    flops = 2.0 * batch * inputs * outputs
+    nbytes = 4.0 * (x.numel() + y.numel() + outputs * inputs)
+    plan.close()
+    return dict(op="fc", batch=batch, inputs=inputs, outputs=outputs, math=math, ms=round(ms, 4),
+                tflops=round(flops / ms / 1e9, 1), gbs=round(nbytes / ms / 1e6, 1))
+
+
+SWEEP = [(256, 56, 256, 3, 1), (512, 14, 512, 3, 1), (64, 56, 256, 1, 0)]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("op", choices=["conv", "fc", "sweep", "vgg"])
+    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--channels", type=int, default=256)
+    ap.add_argument("--size", type=int, default=56)
+    ap.add_argument("--filters", type=int, default=256)
+    ap.add_argument("--k", type=int, default=3)
+    ap.add_argument("--stride", type=int, default=1)
+    ap.add_argument("--pad", type=int, default=1)
+    ap.add_argument("--inputs", type=int, default=4096)
+    ap.add_argument("--outputs", type=int, default=4096)
+    ap.add_argument("--math", default="tf32")
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    a = ap.parse_args()
+    h = api.Handle(0, a.math)
+    if a.op == "conv":
+        print(json.dumps(bench_conv(h, a.batch, a.channels, a.size, a.filters, a.k, a.stride, a.pad, a.math, a.iters, a.warmup)))
+    elif a.op == "fc":
+        print(json.dumps(bench_fc(h, a.batch, a.inputs, a.outputs, a.math, a.iters, a.warmup)))
+    elif a.op == "sweep":
+        for c, s, f, k, p in SWEEP:
+            print(json.dumps(bench_conv(h, a.batch, c, s, f, k, 1, p, a.math, a.iters, a.warmup)), flush=True)
+    else:   # the distinct VGG-16 convolution shapes at the given batch
+        for c, s, f in [(64, 224, 64), (64, 112, 128), (128, 112, 128), (128, 56, 256), (256, 56, 256), (256, 28, 512),
+                        (512, 28, 512), (512, 14, 512)]:
+            print(json.dumps(bench_conv(h, a.batch, c, s, f, 3, 1, 1, a.math, a.iters, a.warmup)), flush=True)
+    h.close()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,32 @@
+"""Small networks shared by the CPU and GPU tests (built with the same builders
+as the benchmark configurations)."""
+from nebula_b200.workloads import NetBuilder, alexnet, lstm2, resnet50, vgg16
+
+
+def toy_convnet(batch=3):
+    """Every layer kind of the convolutional networks, odd extents, 3-channel input."""
+    b = NetBuilder("toy", batch, 3, 19, 17, bias_init="bias_n01")
+    b.conv(32, 3, 1, 1, "leaky", bn=True).maxpool(2, 2, 0).conv(48, 5, 2, 2, "relu").maxpool(3, 2)
+    b.conv(64, 1, 1, 0, "linear", bn=True).conv(64, 3, 1, 1, "leaky", bn=True).conv(64, 1, 1, 0, "linear")
+    b.shortcut(3, "leaky").avgpool(2, 2, 0)
+    b.connected(40, "tanh").dropout().connected(24, "logistic", bn=True).connected(10, "linear").softmax()
+    return b.build()
+
+
+def tiny_vgg(batch=4):
+    return vgg16(batch=batch, height=32, width=32, fc=128, classes=10, widths=(32, 32, 64, 64, 64))
+
+
+def tiny_resnet(batch=2):
+    return resnet50(batch=batch, height=64, width=64, base=32, blocks=(2, 2, 2, 2), classes=10)
+
+
+def tiny_lstm(batch=4, time_steps=6):
+    return lstm2(batch=batch, time_steps=time_steps, input_size=64, hidden=32, classes=50)
+
+
+def small_alexnet(batch=2):
+    return alexnet(batch=batch)
+
+
+NETS = {"toy": toy_convnet, "tiny_vgg": tiny_vgg, "tiny_resnet": tiny_resnet, "tiny_lstm": tiny_lstm}
