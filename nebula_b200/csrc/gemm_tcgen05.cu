@@ -615,7 +615,7 @@ void gemm_tc(nb_handle_s *h, const GemmArgs &a, bool three_pass) {
         encode(h, &p.tm_y, a.y, 4, dims, strides, bx, es);
     }
 
-    ProfileScope prof(h, 0, 2.0 * (double)a.M * a.N * a.Kc * taps);
+    ProfileScope prof(h, 0, a.algo_flops > 0 ? a.algo_flops : 2.0 * (double)a.M * a.N * a.Kc * taps);
     if (three_pass) {
         if (block_n == 128) launch<128, true>(h, p);
         else launch<64, true>(h, p);

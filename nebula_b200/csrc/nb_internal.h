@@ -114,6 +114,7 @@ struct GemmArgs {
     bool round_out_tf32 = false;    // store RN(TF32) values (the consumer is a TF32 contraction)
     float *y = nullptr;
     long ldy = 0;
+    double algo_flops = 0;          // algorithmic FLOPs of this launch for profiling (0: 2*M*N*Kc*taps)
 };
 
 // Tensor-core path (tcgen05 + TMA).  Throws nb::Error(NB_ERR_UNSUPPORTED) when the
@@ -143,6 +144,9 @@ void launch_shortcut(nb_handle_s *h, const nb_shortcut_desc_t &d, const float *p
                      bool round_tf32);
 // weights OIHW [F,C,k,k] -> [k*k][F][Cp] (Cp >= C, zero padded), optionally permuting FC columns
 void launch_weight_relayout(nb_handle_s *h, const float *w_oihw, float *dst, int F, int C, int k, int Cp);
+// explicit patch matrix [pixels][Kpad] (column = (kh,kw,c)) and the matching weight layout [F][Kpad]
+void launch_pack_patches(nb_handle_s *h, const float *x, float *out, const ConvGeom &g, int Kpad, bool round_tf32);
+void launch_weight_pack(nb_handle_s *h, const float *w_oihw, float *dst, int F, int C, int k, int Kpad);
 // FC weights whose columns index (c,h,w) -> columns indexing (h,w,c)
 void launch_fc_permute(nb_handle_s *h, const float *w, float *dst, int out, int C, int H, int W);
 // LSTM cell: z [B,4H] (gate blocks i,f,g,o) -> c_t, h_t (+ TF32-rounded copy of h_t)

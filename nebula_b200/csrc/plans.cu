@@ -58,6 +58,9 @@ ConvPlan::ConvPlan(nb_handle_s *hh, const nb_conv2d_desc_t &desc) : nb_plan_s(NB
     OH = (d.height + 2 * d.padding - d.size) / d.stride + 1;
     OW = (d.width + 2 * d.padding - d.size) / d.stride + 1;
     Cp = (d.channels + 3) / 4 * 4;
+    const int K = d.channels * d.size * d.size;
+    Kpad = (K + 31) / 32 * 32;
+    pack_ok = (Cp != d.channels || d.channels < 32) && Kpad <= 2048;
 }
 
 void ConvPlan::set_weights(const float *weight, const float *bias, const float *g, const float *m, const float *v,
@@ -70,6 +73,11 @@ void ConvPlan::set_weights(const float *weight, const float *bias, const float *
     w.exact.alloc((size_t)d.size * d.size * d.filters * Cp);
     w.split_ready = false;
     launch_weight_relayout(h, raw.p, w.exact.p, d.filters, d.channels, d.size, Cp);
+    if (pack_ok) {
+        wp.exact.alloc((size_t)d.filters * Kpad);
+        wp.split_ready = false;
+        launch_weight_pack(h, raw.p, wp.exact.p, d.filters, d.channels, d.size, Kpad);
+    }
     NB_CHECK_CUDA(cudaStreamSynchronize(h->stream));
     std::vector<float> hb = to_host(h, bias, d.filters, mem), hg, hm, hv, sc, sh;
     if (d.batch_normalize) {
@@ -103,6 +111,36 @@ void ConvPlan::forward(const float *x, float *y, const ForwardOpts &o) {
     ConvGeom &g = a.g;
     g.batch = d.batch; g.C = d.channels; g.H = d.height; g.W = d.width; g.OH = OH; g.OW = OW;
     g.ksize = d.size; g.stride = d.stride; g.pad = d.padding;
+
+    if (pth == PATH_SIMT && pack_ok && h->math_mode != NB_MATH_FP32 && h->encode_tiled) {
+        // tensor-core route for small channel counts: pack patches, then a plain GEMM
+        const bool three = h->math_mode == NB_MATH_TF32X3;
+        const size_t M = (size_t)d.batch * OH * OW;
+        if (o.x_nhwc) {
+            g.sc = 1; g.sw = d.channels; g.sh = (long)d.width * d.channels; g.sn = (long)d.height * d.width * d.channels;
+        } else {
+            g.sw = 1; g.sh = d.width; g.sc = (long)d.height * d.width; g.sn = (long)d.channels * d.height * d.width;
+        }
+        if (x_scratch.n < M * Kpad) x_scratch.alloc(M * Kpad);
+        launch_pack_patches(h, x, x_scratch.p, g, Kpad, !three);
+        GemmArgs pa;
+        pa.a = x_scratch.p; pa.lda = Kpad; pa.ldb = Kpad; pa.M = (int)M; pa.N = d.filters; pa.Kc = Kpad;
+        pa.scale = has_scale ? scale.p : nullptr; pa.shift = shift.p; pa.act = d.activation;
+        pa.round_out_tf32 = o.round_out; pa.addend = o.addend; pa.ld_addend = d.filters;
+        float *yo = y;
+        if (!o.y_nhwc) {
+            NB_REQUIRE(o.addend == nullptr, "conv: addend needs NHWC output");
+            if (y_scratch.n < yout) y_scratch.alloc(yout);
+            yo = y_scratch.p;
+        }
+        pa.y = yo; pa.ldy = d.filters;
+        pa.algo_flops = 2.0 * (double)M * d.filters * d.channels * d.size * d.size;
+        wp.ensure_split(h);
+        pa.b = wp.hi.p; pa.b_lo = wp.lo.p;
+        gemm_tc(h, pa, three);
+        if (!o.y_nhwc) launch_layout(h, yo, y, d.batch, d.filters, OH, OW, false, false);
+        return;
+    }
 
     const float *xa = x;
     bool nhwc = o.x_nhwc;

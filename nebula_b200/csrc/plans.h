@@ -52,6 +52,11 @@ struct ConvPlan : nb_plan_s {
     nb_conv2d_desc_t d;
     int OH, OW, Cp;
     WeightSet w;                    // [tap][F][Cp]
+    // Small channel counts (3-channel input layers) cannot be addressed by TMA boxes:
+    // their patches are packed into an explicit [pixels][Kpad] matrix instead.
+    bool pack_ok = false;
+    int Kpad = 0;
+    WeightSet wp;                   // [F][Kpad], column = (kh,kw,c)
     DeviceBuffer scale, shift;
     bool has_scale = false, ready = false;
     DeviceBuffer x_scratch, y_scratch;
