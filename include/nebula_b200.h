@@ -126,6 +126,20 @@ int nb_fc_set_weights(nb_plan_t plan, const float *weight, const float *bias, co
  * Also serves connected_layer_t::_forward_(float*) (connected_layer.cu:50-88). */
 int nb_fc_forward(nb_plan_t plan, const float *x, float *y);
 
+/* Connected-layer forward that allocates nothing (no counterpart in the
+ * reference).  For callers that must not allocate device memory while running:
+ * a serving loop whose device memory all belongs to another allocator, or a phase
+ * where cudaMalloc's device-wide synchronisation (or its failure) is unacceptable.
+ * y[batch,outputs] = act(x[batch,inputs] * weight[outputs,inputs]^T + bias); all
+ * pointers are device pointers, no batch-norm.  Working copies (TF32-rounded
+ * operands, or the 3xTF32 weight split) live in a 16 MiB array built into the
+ * library: batch*inputs + outputs*inputs floats (2*outputs*inputs for 3xTF32) must
+ * fit in 4 Mi floats, else NB_ERR_INVALID_ARG.  The first call on a device looks
+ * the array's device address up and should be made before any stream capture
+ * begins.  All calls share the array: calls that overlap on the GPU race. */
+int nb_fc_forward_static(nb_handle_t handle, const float *x, const float *weight, const float *bias, int batch,
+                         int inputs, int outputs, int activation, float *y);
+
 /* ------------------------------------------------------------------ pooling */
 /* pooling_layer_t::init / _forward_ (pooling_layer.cc:40-63, pooling_layer.cu:150-175),
  * output extent (H+2p)/stride, max identity -1e8, average divisor size*size. */

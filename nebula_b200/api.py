@@ -92,6 +92,7 @@ SIGNATURES = {
     "nb_fc_plan_create": (C.c_int, [_VP, C.POINTER(FcDesc), C.POINTER(_VP)]),
     "nb_fc_set_weights": (C.c_int, [_VP, _VP, _VP, _VP, _VP, _VP, C.c_int]),
     "nb_fc_forward": (C.c_int, [_VP, _VP, _VP]),
+    "nb_fc_forward_static": (C.c_int, [_VP, _VP, _VP, _VP, C.c_int, C.c_int, C.c_int, C.c_int, _VP]),
     "nb_pool_forward": (C.c_int, [_VP, C.POINTER(PoolDesc), _VP, _VP]),
     "nb_shortcut_forward": (C.c_int, [_VP, C.POINTER(ShortcutDesc), _VP, _VP, _VP]),
     "nb_lstm_plan_create": (C.c_int, [_VP, C.POINTER(LstmDesc), C.POINTER(_VP)]),
@@ -248,6 +249,17 @@ class Handle:
     def batchnorm_scale_down(self, out, scale, channel, size, batch):
         self.check(self.lib.nb_batchnorm_scale_down(self.h, _ptr(out), _ptr(scale), channel, size, batch))
         return out
+
+    def fc_forward_static(self, x, weight, bias, activation="linear"):
+        """Connected-layer forward through the entry point that allocates nothing
+        (its scratch is a fixed array inside the library); device tensors only."""
+        import torch
+        batch, inputs = x.shape
+        outputs = weight.shape[0]
+        y = torch.empty((batch, outputs), device=x.device, dtype=torch.float32)
+        self.check(self.lib.nb_fc_forward_static(self.h, _ptr(x), _ptr(weight), _ptr(bias), batch, inputs, outputs,
+                                                 ACT[activation], _ptr(y)))
+        return y
 
     def softmax(self, x):
         import torch
