@@ -217,6 +217,12 @@ int nb_network_forward(nb_network_t net, const float *input);
  * output (see nb_network_output) back; the call returns with `output` filled. */
 int nb_network_forward_host(nb_network_t net, const float *input_host, float *output_host);
 
+/* Layer fusion (default on): a 2x2 stride-2 max-pool that follows a convolution is
+ * computed in that convolution's epilogue, so the convolution's own output_data is
+ * never written and nb_network_layer_output refuses it.  Turn fusion off to
+ * materialise every layer's output as the reference does (no reference counterpart). */
+int nb_network_set_fusion(nb_network_t net, int enable);
+
 typedef struct {
     int type;                   /* the reference's layer_type_t code (common/def.h:28-42) */
     int channels, height, width;

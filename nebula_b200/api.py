@@ -112,6 +112,7 @@ SIGNATURES = {
     "nb_network_weight_count": (C.c_size_t, [_VP]),
     "nb_network_forward": (C.c_int, [_VP, _VP]),
     "nb_network_forward_host": (C.c_int, [_VP, _VP, _VP]),
+    "nb_network_set_fusion": (C.c_int, [_VP, C.c_int]),
     "nb_network_num_layers": (C.c_int, [_VP]),
     "nb_network_layer_info": (C.c_int, [_VP, C.c_int, C.POINTER(LayerInfo)]),
     "nb_network_layer_output": (C.c_int, [_VP, C.c_int, _VP, C.c_int]),
@@ -381,6 +382,10 @@ class Network:
 
     def load_weight_file(self, path):
         self.handle.check(self.handle.lib.nb_network_load_weight_file(self.n, str(path).encode()))
+
+    def set_fusion(self, enable: bool):
+        """Fusion on (default): conv + 2x2/2 max-pool run as one kernel and the conv's own output is not kept."""
+        self.handle.check(self.handle.lib.nb_network_set_fusion(self.n, int(enable)))
 
     def layer_info(self, i):
         info = LayerInfo()

@@ -401,6 +401,11 @@ int nb_network_forward_host(nb_network_t net, const float *input_host, float *ou
         net->layer_output(-1, output_host, NB_MEM_HOST);
     });
 }
+int nb_network_set_fusion(nb_network_t net, int enable) {
+    if (!net) return NB_ERR_INVALID_ARG;
+    net->fuse = enable != 0;
+    return NB_OK;
+}
 int nb_network_num_layers(nb_network_t net) { return net ? (int)net->layers.size() : -1; }
 int nb_network_layer_info(nb_network_t net, int index, nb_layer_info_t *info) {
     if (!net || !info) return NB_ERR_INVALID_ARG;

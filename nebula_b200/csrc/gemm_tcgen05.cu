@@ -53,6 +53,7 @@ struct TcParams {
     CUtensorMap tm_b;
     CUtensorMap tm_b_lo;
     CUtensorMap tm_y;
+    CUtensorMap tm_yp;          // 2x2/2 max-pooled output (pool mode)
     // tiling of the M dimension into (bw x bh x bn) boxes of output pixels
     int bw, bh, bn;
     int tiles_w, tiles_h, tiles_n;
@@ -70,6 +71,7 @@ struct TcParams {
     float *y;
     long ldy;
     int tma_store;              // y meets TMA's rules: tiles leave through tm_y; else plain stores
+    int pool;                   // fuse the following 2x2 stride-2 max-pool: only the pooled tensor is written
     int *status;
 };
 
@@ -402,7 +404,46 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
 #pragma unroll
                     for (int j = 0; j < 32; j++) v[j] = __float_as_uint(round_tf32(__uint_as_float(v[j])));
                 }
-                if (p.tma_store) {
+                if (p.pool) {
+                    // conv + 2x2/2 max-pool (pooling_layer.cc:117-146): the full-resolution slab stays in
+                    // shared memory (buffer 0); each thread reduces two 16-byte chunks of one pooled pixel
+                    // into one of two small pooled buffers (inside buffer 1), which leaves by TMA.
+                    float4 *slab0 = reinterpret_cast<float4 *>(out_stage);
+                    float4 *pooled = reinterpret_cast<float4 *>(out_stage + C::OUT_STAGE_BYTES + slab * 4096);
+                    if (store_thread) tma_store_wait_read<1>();
+                    epilogue_bar_sync();
+#pragma unroll
+                    for (int j = 0; j < 8; j++)
+                        slab0[r * 8 + (j ^ (r & 7))] = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                                                  __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+                    epilogue_bar_sync();
+                    const int t = threadIdx.x - 64;
+                    const int pr = t >> 2, hw = p.bw >> 1, hh = p.bh >> 1;
+                    const int pw = pr % hw, ph = (pr / hw) % hh, pn = pr / (hw * hh);
+                    if (pn < p.bn) {
+                        const int r00 = (pn * p.bh + 2 * ph) * p.bw + 2 * pw;
+#pragma unroll
+                        for (int e = 0; e < 2; e++) {
+                            const int c = (t & 3) * 2 + e;
+                            float4 m = make_float4(-1e8f, -1e8f, -1e8f, -1e8f);     // the reference's identity
+#pragma unroll
+                            for (int w4 = 0; w4 < 4; w4++) {
+                                const int rr = r00 + (w4 >> 1) * p.bw + (w4 & 1);
+                                const float4 x4 = slab0[rr * 8 + (c ^ (rr & 7))];
+                                m.x = x4.x > m.x ? x4.x : m.x; m.y = x4.y > m.y ? x4.y : m.y;
+                                m.z = x4.z > m.z ? x4.z : m.z; m.w = x4.w > m.w ? x4.w : m.w;
+                            }
+                            pooled[pr * 8 + (c ^ (pr & 7))] = m;
+                        }
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    epilogue_bar_sync();
+                    if (store_thread) {
+                        tma_store_4d(&p.tm_yp, pooled, col0, tw * hw, th * hh, tn * p.bn);
+                        tma_store_commit();
+                    }
+                    slab ^= 1;
+                } else if (p.tma_store) {
                     // the store issued two slabs ago must have finished reading this buffer
                     if (store_thread) tma_store_wait_read<1>();
                     epilogue_bar_sync();
@@ -482,7 +523,7 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
 struct Box { int bw, bh, bn; };
 
 // Chooses the (bw x bh x bn) pixel box (<= 128 rows) that wastes the fewest MMA rows.
-Box choose_box(int OW, int OH, int NB, int stride) {
+Box choose_box(int OW, int OH, int NB, int stride, bool even) {
     Box best{1, 1, 1};
     double best_eff = -1;
     const int max_dim = 256 / std::max(1, stride);     // TMA box extent limit (elements traversed)
@@ -491,6 +532,7 @@ Box choose_box(int OW, int OH, int NB, int stride) {
         for (int bh = 1; bh <= std::min({OH, rem, max_dim}); bh++) {
             const int bn = std::min({NB, 128 / (bw * bh), 256});
             if (bn < 1) continue;
+            if (even && ((bw | bh) & 1)) continue;      // 2x2 pooling windows must not straddle tiles
             auto eff1 = [](int ext, int b) { return (double)ext / ((double)((ext + b - 1) / b) * b); };
             double eff = eff1(OW, bw) * eff1(OH, bh) * eff1(NB, bn) * (double)(bw * bh * bn) / 128.0;
             // prefer wider boxes on ties (longer contiguous runs per TMA request)
@@ -560,7 +602,8 @@ void gemm_tc(nb_handle_s *h, const GemmArgs &a, bool three_pass) {
         g.sc = 1; g.sw = a.lda; g.sh = (long)a.lda * a.M; g.sn = (long)a.lda * a.M;
     }
     const int taps = g.ksize * g.ksize;
-    Box box = choose_box(g.OW, g.OH, g.batch, g.stride);
+    const bool pool = a.y_pool != nullptr;
+    Box box = choose_box(g.OW, g.OH, g.batch, g.stride, pool);
     p.bw = box.bw; p.bh = box.bh; p.bn = box.bn;
     p.tiles_w = (g.OW + box.bw - 1) / box.bw;
     p.tiles_h = (g.OH + box.bh - 1) / box.bh;
@@ -575,7 +618,15 @@ void gemm_tc(nb_handle_s *h, const GemmArgs &a, bool three_pass) {
     p.scale = a.scale; p.shift = a.shift; p.addend = a.addend; p.ld_addend = a.ld_addend;
     p.act = a.act; p.round_out = a.round_out_tf32 ? 1 : 0;
     p.y = a.y; p.ldy = a.ldy;
-    p.tma_store = aligned16(a.y) && (a.ldy % 4) == 0;
+    p.tma_store = a.y && aligned16(a.y) && (a.ldy % 4) == 0;
+    p.pool = pool ? 1 : 0;
+    if (pool) {
+        if (!a.a_is_conv || (g.OW & 1) || (g.OH & 1) || (a.N % 4) || !aligned16(a.y_pool) || a.addend)
+            throw Error(NB_ERR_UNSUPPORTED, "fused 2x2 pooling needs even output extents and a 16-byte aligned NHWC tensor");
+        p.tma_store = 0;
+    } else if (!a.y) {
+        throw Error(NB_ERR_INVALID_ARG, "GEMM without an output tensor");
+    }
     p.status = h->d_status;
 
     // tile width in filters: widest tile that still gives every SM work
@@ -613,6 +664,15 @@ void gemm_tc(nb_handle_s *h, const GemmArgs &a, bool three_pass) {
         cuuint32_t bx[4] = {32, (cuuint32_t)box.bw, (cuuint32_t)box.bh, (cuuint32_t)box.bn};
         cuuint32_t es[4] = {1, 1, 1, 1};
         encode(h, &p.tm_y, a.y, 4, dims, strides, bx, es);
+    }
+
+    if (pool) {          // pooled Y: dims {N, OW/2, OH/2, NB}
+        cuuint64_t dims[4] = {(cuuint64_t)a.N, (cuuint64_t)(g.OW / 2), (cuuint64_t)(g.OH / 2), (cuuint64_t)g.batch};
+        cuuint64_t strides[3] = {(cuuint64_t)a.N * 4, (cuuint64_t)a.N * 4 * (cuuint64_t)(g.OW / 2),
+                                 (cuuint64_t)a.N * 4 * (cuuint64_t)(g.OW / 2) * (cuuint64_t)(g.OH / 2)};
+        cuuint32_t bx[4] = {32, (cuuint32_t)(box.bw / 2), (cuuint32_t)(box.bh / 2), (cuuint32_t)box.bn};
+        cuuint32_t es[4] = {1, 1, 1, 1};
+        encode(h, &p.tm_yp, a.y_pool, 4, dims, strides, bx, es);
     }
 
     ProfileScope prof(h, 0, a.algo_flops > 0 ? a.algo_flops : 2.0 * (double)a.M * a.N * a.Kc * taps);

@@ -114,6 +114,8 @@ struct GemmArgs {
     bool round_out_tf32 = false;    // store RN(TF32) values (the consumer is a TF32 contraction)
     float *y = nullptr;
     long ldy = 0;
+    // tensor-core conv only: write the 2x2 stride-2 max-pooled output [B][OH/2][OW/2][N] here INSTEAD of y
+    float *y_pool = nullptr;
     double algo_flops = 0;          // algorithmic FLOPs of this launch for profiling (0: 2*M*N*Kc*taps)
 };
 

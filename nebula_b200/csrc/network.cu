@@ -289,6 +289,25 @@ void nb_network_s::forward(const float *input) {
             case LT_CONVOLUTIONAL: {
                 ForwardOpts o;
                 o.x_nhwc = cur_nhwc; o.y_nhwc = true; o.x_rounded = cur_rounded; o.round_out = round_out;
+                l.materialised = true;
+                // conv -> maxpool 2x2/2: the pooled tensor is produced by the conv epilogue
+                bool referenced = false;        // a later shortcut reads this layer's own output
+                for (int j = i + 2; j < n; j++) referenced |= layers[j]->type == LT_SHORTCUT && layers[j]->conn == i;
+                if (fuse && !referenced && i + 1 < n && layers[i + 1]->type == LT_MAXPOOL && l.conv->can_fuse_pool()) {
+                    const nb_pool_desc_t &pd = layers[i + 1]->pool;
+                    if (pd.size == 2 && pd.stride == 2 && pd.padding == 0) {
+                        NetLayer &pl = *layers[i + 1];
+                        const bool pool_round = consumer_is_tf32(i + 1);
+                        o.round_out = pool_round;
+                        o.pool_out = pl.out_ptr;
+                        l.conv->forward(cur, nullptr, o);
+                        l.materialised = false;
+                        pl.out_is_rounded = pool_round;
+                        cur = pl.out_ptr; cur_nhwc = true; cur_rounded = pool_round; cur_round = nullptr;
+                        i++;            // the pooling layer is done
+                        continue;
+                    }
+                }
                 l.conv->forward(cur, l.out_ptr, o);
                 break;
             }
@@ -349,6 +368,9 @@ void nb_network_s::layer_output(int index, float *dst, int mem) {
     NB_REQUIRE(index >= 0 && index < n, "layer index out of range");
     NB_REQUIRE(dst != nullptr, "null destination");
     NetLayer &l = *layers[index];
+    if (!l.materialised)
+        throw Error(NB_ERR_UNSUPPORTED, "this layer's output was fused into the next layer's; disable fusion "
+                                        "(nb_network_set_fusion) to materialise it");
     const size_t total = l.size * rows;
     const float *src = l.out_ptr;
     if (l.nhwc && l.H * l.W > 1 && l.C > 1) {

@@ -48,6 +48,7 @@ struct NetLayer {
     nb_shortcut_desc_t shortcut;
     int conn = -1;                      // shortcut: index of the connected layer
     size_t weight_floats = 0;
+    bool materialised = true;           // false while this layer's own buffer is skipped by a fusion
 };
 
 }  // namespace nb
@@ -63,6 +64,7 @@ struct nb_network_s {
     nb::DeviceBuffer input_dev, input_nhwc, convert_tmp;
     int logits_layer = -1;
     bool weights_loaded = false;
+    bool fuse = true;                   // fold 2x2/2 max-pools into the preceding convolution's epilogue
 
     size_t weight_count() const;
     void build(const std::string &cfg_text, int batch_override);

@@ -99,9 +99,14 @@ GemmPath ConvPlan::path(const ForwardOpts &) const {
     return h->math_mode == NB_MATH_TF32X3 ? PATH_TC3 : PATH_TC;
 }
 
+bool ConvPlan::can_fuse_pool() const {
+    const GemmPath pth = path(ForwardOpts());
+    return (pth == PATH_TC || pth == PATH_TC3) && !(OH & 1) && !(OW & 1) && (d.filters % 4) == 0 && OH >= 2 && OW >= 2;
+}
+
 void ConvPlan::forward(const float *x, float *y, const ForwardOpts &o) {
     if (!ready) throw Error(NB_ERR_NO_WEIGHTS, "conv: forward before set_weights");
-    NB_REQUIRE(x && y, "conv: null tensor pointer");
+    NB_REQUIRE(x && (y || o.pool_out), "conv: null tensor pointer");
     const GemmPath pth = path(o);
     const size_t xin = (size_t)d.batch * d.channels * d.height * d.width;
     const size_t yout = (size_t)d.batch * d.filters * OH * OW;
@@ -181,6 +186,11 @@ void ConvPlan::forward(const float *x, float *y, const ForwardOpts &o) {
     }
     a.y = yo;
     a.ldy = d.filters;
+    if (o.pool_out) {
+        NB_REQUIRE(o.y_nhwc && pth != PATH_SIMT, "conv: fused pooling needs the tensor-core path and NHWC output");
+        a.y = nullptr;
+        a.y_pool = o.pool_out;
+    }
     if (pth == PATH_SIMT) {
         a.b = w.exact.p;
         gemm_simt(h, a);

@@ -46,6 +46,7 @@ struct ForwardOpts {
     bool x_rounded = false;         // x already holds TF32-rounded values
     bool round_out = false;         // store TF32-rounded outputs (consumer is a TF32 contraction)
     const float *addend = nullptr;  // optional tensor added before the activation (same layout as y)
+    float *pool_out = nullptr;      // conv: write only the 2x2/2 max-pooled NHWC output here (y is not written)
 };
 
 struct ConvPlan : nb_plan_s {
@@ -65,6 +66,8 @@ struct ConvPlan : nb_plan_s {
     void forward(const float *x, float *y, const ForwardOpts &o);
     void output_dims(int dims[3]) const override { dims[0] = d.filters; dims[1] = OH; dims[2] = OW; }
     GemmPath path(const ForwardOpts &o) const;
+    // can the following 2x2 stride-2 max-pool be done in this layer's epilogue?
+    bool can_fuse_pool() const;
 };
 
 struct FcPlan : nb_plan_s {

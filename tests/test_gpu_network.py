@@ -9,7 +9,7 @@ from tests.util import NET_TOL, assert_close, rel_err
 pytestmark = pytest.mark.gpu
 
 
-def _run(handle, wl, mode, seed=1):
+def _run(handle, wl, mode, seed=1, fusion=False):
     import torch
     from nebula_b200 import api
     handle.set_math(mode)
@@ -17,6 +17,7 @@ def _run(handle, wl, mode, seed=1):
     x = wl.make_input(seed + 1)
     net = api.Network(handle, wl.cfg)
     assert net.weight_count == w.size
+    net.set_fusion(fusion)          # unfused: every layer's output_data is materialised, as in the reference
     net.load_weights(w)
     net.forward(torch.from_numpy(x).cuda())
     handle.synchronize()
@@ -72,6 +73,26 @@ def test_alexnet_full_size_two_images(handle):
         probs = net.output().reshape(2, -1)
         assert np.allclose(probs.sum(1), 1.0, atol=1e-4)
         net.close()
+
+
+@pytest.mark.parametrize("mode", ["tf32", "tf32x3"])
+@pytest.mark.parametrize("name", ["tiny_vgg", "toy"])
+def test_fused_pooling_is_bit_identical(handle, name, mode):
+    """conv + 2x2/2 max-pool in one kernel gives exactly what the two kernels give."""
+    from nebula_b200 import api
+    wl = NETS[name](batch=5)
+    a, w, x = _run(handle, wl, mode, fusion=False)
+    b, _, _ = _run(handle, wl, mode, fusion=True)
+    assert np.array_equal(a.logits(), b.logits())
+    pools = [i for i in range(a.num_layers) if a.layer_info(i)["type"] == "maxpool"]
+    assert pools
+    for i in pools:
+        assert np.array_equal(a.layer_output(i, 5), b.layer_output(i, 5)), f"pool layer {i}"
+    if name == "tiny_vgg":
+        with pytest.raises(api.NebulaError):        # the fused convolution's own output is not kept
+            b.layer_output(pools[0] - 1, 5)
+    a.close()
+    b.close()
 
 
 def test_forward_host_matches_device_path(handle):
