@@ -133,8 +133,8 @@ int nb_fc_forward(nb_plan_t plan, const float *x, float *y);
  * y[batch,outputs] = act(x[batch,inputs] * weight[outputs,inputs]^T + bias); all
  * pointers are device pointers, no batch-norm.  Working copies (TF32-rounded
  * operands, or the 3xTF32 weight split) live in a 16 MiB array built into the
- * library: batch*inputs + outputs*inputs floats (2*outputs*inputs for 3xTF32) must
- * fit in 4 Mi floats, else NB_ERR_INVALID_ARG.  The first call on a device looks
+ * library: batch*inputs + outputs*inputs + outputs floats (2*outputs*inputs + outputs
+ * for 3xTF32) must fit in 4 Mi floats, else NB_ERR_INVALID_ARG.  The first call on a device looks
  * the array's device address up and should be made before any stream capture
  * begins.  All calls share the array: calls that overlap on the GPU race. */
 int nb_fc_forward_static(nb_handle_t handle, const float *x, const float *weight, const float *bias, int batch,

@@ -240,37 +240,7 @@ __global__ void shortcut_kernel(const float *prev, const float *conn, float *y, 
     }
 }
 
-// ------------------------------------------------------------ patch packing
-// Explicit K-major patch matrix for convolutions whose channel count TMA cannot
-// address (3-channel input layers): row m = output pixel, column kk = (kh,kw,c)
-// with c fastest, zero beyond k*k*C up to Kpad.  Four columns per thread, so a
-// warp writes 512 contiguous bytes; the input is read through the cache (each
-// element is used k*k times).
-__global__ void pack_patches_kernel(const float *x, float4 *out, ConvGeom g, int K, int Kpad4, int round, size_t total) {
-    const size_t stride = (size_t)gridDim.x * blockDim.x;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-        const size_t m = i / Kpad4;
-        const int q = (int)(i - m * Kpad4);
-        const int per = g.OH * g.OW;
-        const int n = (int)(m / per), rem = (int)(m - (size_t)n * per);
-        const int oh = rem / g.OW, ow = rem - oh * g.OW;
-        float v[4];
-#pragma unroll
-        for (int e = 0; e < 4; e++) {
-            const int kk = q * 4 + e;
-            float val = 0.0f;
-            if (kk < K) {
-                const int tap = kk / g.C, c = kk - tap * g.C;
-                const int kh = tap / g.ksize, kw = tap - kh * g.ksize;
-                const int ih = oh * g.stride + kh - g.pad, iw = ow * g.stride + kw - g.pad;
-                if (ih >= 0 && ih < g.H && iw >= 0 && iw < g.W)
-                    val = __ldg(x + (long)n * g.sn + (long)c * g.sc + (long)ih * g.sh + (long)iw * g.sw);
-            }
-            v[e] = round ? round_tf32(val) : val;
-        }
-        out[i] = make_float4(v[0], v[1], v[2], v[3]);
-    }
-}
+// ---------------------------------------------------- gathered-A weight layout
 // OIHW [F][C][k][k] -> [F][Kpad] with column (tap*C + c), zero padded
 __global__ void weight_pack_kernel(const float *w, float *dst, int F, int C, int k, int Kpad, size_t total) {
     const size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -471,14 +441,6 @@ void launch_shortcut(nb_handle_s *h, const nb_shortcut_desc_t &d, const float *p
             prev, conn, y, d.batch, d.conn_channels, d.conn_height, d.conn_width, d.out_channels, d.out_height,
             d.out_width, stride, sample, d.activation, round ? 1 : 0, total);
     check_launch("shortcut_kernel");
-    count_launch(h);
-}
-void launch_pack_patches(nb_handle_s *h, const float *x, float *out, const ConvGeom &g, int Kpad, bool round) {
-    const size_t total = (size_t)g.batch * g.OH * g.OW * (Kpad / 4);
-    if (!total) return;
-    pack_patches_kernel<<<grid_for(total, h), TPB, 0, h->stream>>>(x, (float4 *)out, g, g.ksize * g.ksize * g.C, Kpad / 4,
-                                                                    round ? 1 : 0, total);
-    check_launch("pack_patches_kernel");
     count_launch(h);
 }
 void launch_weight_pack(nb_handle_s *h, const float *w, float *dst, int F, int C, int k, int Kpad) {

@@ -20,11 +20,12 @@
 //     TF32 rounding for the next contraction, and stores NHWC rows directly.
 // A plain row-major matrix is the special case "image of height 1, 1x1 filter".
 //
-// Warp roles (192 threads; 320 in three-pass mode):
+// Warp roles (320 threads; 448 with the extra operand warps):
 //   warp 0      TMA producer (one elected lane)
 //   warp 1      TMEM allocation + MMA issue (one elected lane)
 //   warps 2-5   epilogue (TMEM -> registers -> global)
-//   warps 6-9   three-pass mode only: split each A tile into hi/lo TF32 terms
+//   warps 10-13 three-pass mode: split each A tile into hi/lo TF32 terms; gather mode: build the
+//               A tile in shared memory from a strided tensor (3-channel input layers)
 //
 // Every wait is bounded: a wait that runs out sets the CTA's abort flag and the
 // device status word, all roles drain, TMEM is freed and the kernel returns.
@@ -65,13 +66,21 @@ struct TcParams {
     int N;                      // valid output columns
     int tx_bytes_a;             // bytes one A box load delivers
     // epilogue
-    const float *scale, *shift, *addend;
+    const float *scale, *shift, *addend;    // scale/shift readable up to the next multiple of 32 columns
     long ld_addend;
+    int addend_vec;             // addend rows are 16-byte aligned
     int act, round_out;
     float *y;
     long ldy;
     int tma_store;              // y meets TMA's rules: tiles leave through tm_y; else plain stores
     int pool;                   // fuse the following 2x2 stride-2 max-pool: only the pooled tensor is written
+    // gather mode: warps 6-9 build the A tile in shared memory from a strided activation tensor
+    // (channel counts TMA cannot address, e.g. the 3-channel input layer); rows are output pixels
+    int gather;
+    const float *gx;
+    const int2 *gtab;           // per column kk: {element offset of (c, kh-pad, kw-pad), (kh-pad) | (kw-pad) << 16}
+    long gsn, gsh, gsw;
+    int gH, gW, gOH, gOW, gstride, gM, ground;
     int *status;
 };
 
@@ -150,18 +159,19 @@ __device__ __forceinline__ void tma_store_wait_read() {
     asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
 }
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-__device__ __forceinline__ void epilogue_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
-// AND-vote across the 128 epilogue threads (named barrier 1), so that leaving the tile
-// loop is a uniform decision and no thread is left alone at a later bar.sync.
-__device__ __forceinline__ bool epilogue_all(bool pred) {
+// named barrier `id` over the 128 threads of one epilogue group
+__device__ __forceinline__ void epilogue_bar_sync(int id) { asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory"); }
+// AND-vote across the 128 threads of an epilogue group (named barrier `id`), so that leaving
+// the tile loop is a uniform decision and no thread is left alone at a later bar.sync.
+__device__ __forceinline__ bool epilogue_all(bool pred, int id) {
     uint32_t r;
     asm volatile(
         "{\n\t.reg .pred p, q;\n\t"
         "setp.ne.b32 p, %1, 0;\n\t"
-        "bar.red.and.pred q, 1, 128, p;\n\t"
+        "bar.red.and.pred q, %2, 128, p;\n\t"
         "selp.b32 %0, 1, 0, q;\n\t}"
         : "=r"(r)
-        : "r"((uint32_t)pred)
+        : "r"((uint32_t)pred), "r"(id)
         : "memory");
     return r != 0;
 }
@@ -222,14 +232,14 @@ struct Cfg {
     static constexpr int STAGE_BYTES = (A_STAGE_BYTES + B_STAGE_BYTES) * (THREE ? 2 : 1);
     static constexpr int STAGES = (196 * 1024) / STAGE_BYTES < 8 ? (196 * 1024) / STAGE_BYTES : 8;
     static constexpr int TMEM_COLS = 2 * BLOCK_N;
-    static constexpr int THREADS = THREE ? 320 : 192;
+    static constexpr int MAX_THREADS = 448;
     static constexpr int OUT_STAGE_BYTES = BLOCK_M * 32 * 4;     // one 128 x 32 output slab
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 2 * OUT_STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
 };
 
 // ------------------------------------------------------------------- kernel
 template <int BLOCK_N, bool THREE>
-__global__ void __launch_bounds__(Cfg<BLOCK_N, THREE>::THREADS, 1)
+__global__ void __launch_bounds__(Cfg<BLOCK_N, THREE>::MAX_THREADS, 1)
 gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
     using C = Cfg<BLOCK_N, THREE>;
     constexpr int STAGES = C::STAGES;
@@ -252,13 +262,13 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
-            mbar_init(&full[s], 1);
+            mbar_init(&full[s], p.gather ? 129 : 1);
             mbar_init(&empty[s], 1);
             mbar_init(&split[s], 128);
         }
         for (int a = 0; a < 2; a++) {
             mbar_init(&acc_full[a], 1);
-            mbar_init(&acc_empty[a], 128);
+            mbar_init(&acc_empty[a], 256);
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -294,8 +304,8 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
                     const int kh = tap / p.ksize, kw = tap - kh * p.ksize;
                     uint8_t *sa = smem + stage * C::STAGE_BYTES;
                     uint8_t *sb = sa + A_STAGE_BYTES;
-                    mbar_expect_tx(&full[stage], (uint32_t)(p.tx_bytes_a + C::B_STAGE_BYTES * (THREE ? 2 : 1)));
-                    tma_load_4d(sa, &p.tm_a, &full[stage], cb * BLOCK_K, w0 + kw, h0 + kh, n0);
+                    mbar_expect_tx(&full[stage], (uint32_t)((p.gather ? 0 : p.tx_bytes_a) + C::B_STAGE_BYTES * (THREE ? 2 : 1)));
+                    if (!p.gather) tma_load_4d(sa, &p.tm_a, &full[stage], cb * BLOCK_K, w0 + kw, h0 + kh, n0);
                     tma_load_3d(sb, &p.tm_b, &full[stage], cb * BLOCK_K, n_tile * BLOCK_N, tap);
                     if (THREE)
                         tma_load_3d(sb + C::B_STAGE_BYTES + A_STAGE_BYTES, &p.tm_b_lo, &full[stage], cb * BLOCK_K,
@@ -319,7 +329,7 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BLOCK_N);
                 for (int kb = 0; kb < p.num_k_blocks; kb++) {
-                    uint64_t *ready = THREE ? &split[stage] : &full[stage];
+                    uint64_t *ready = (THREE && !p.gather) ? &split[stage] : &full[stage];
                     if (!(ok = mbar_wait(ready, phase, abort_flag, p.status))) break;
                     tc_fence_after();
                     const uint32_t sa = smem_u32(smem + stage * C::STAGE_BYTES);
@@ -347,15 +357,22 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
             }
         }
         __syncwarp();
-    } else if (warp < 6) {
+    } else if (warp < 10) {
         // ---------------------------------------------------------- epilogue
+        // Two groups of four warps; group g owns the 32-column slabs of parity g, its own staging
+        // buffer, named barrier and TMA-store thread, so two slabs are in flight per tile and every
+        // scheduler has two epilogue warps to alternate between.
+        const int ew = warp - 2;                // 0..7
+        const int grp = ew >> 2;
+        const int bar_id = 1 + grp;
         const int q = warp & 3;                 // TMEM lane quarter this warp may read
         const int r = q * 32 + lane;            // row inside the tile
+        const int t = (ew & 3) * 32 + lane;     // index inside the group
         const int rw = r % p.bw, rh = (r / p.bw) % p.bh, rn = r / (p.bw * p.bh);
-        const bool store_thread = threadIdx.x == 64;
+        const bool store_thread = t == 0;
+        float4 *slab = reinterpret_cast<float4 *>(out_stage + grp * C::OUT_STAGE_BYTES);
         int acc = 0;
         uint32_t acc_phase = 0;
-        int slab = 0;                           // output staging buffer in use
         bool ok = true;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
             const int m_tile = tile / p.n_tiles, n_tile = tile % p.n_tiles;
@@ -365,26 +382,53 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
             const int ow = tw * p.bw + rw, oh = th * p.bh + rh, n = tn * p.bn + rn;
             const bool row_ok = (rn < p.bn) && ow < p.OW && oh < p.OH && n < p.NB;
             const long row = ((long)n * p.OH + oh) * p.OW + ow;
-            if (!(ok = epilogue_all(mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status)))) break;
+            if (!(ok = epilogue_all(mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status), bar_id))) break;
             tc_fence_after();
 #pragma unroll 1
-            for (int chunk = 0; chunk < BLOCK_N / 32; chunk++) {
+            for (int chunk = grp; chunk < BLOCK_N / 32; chunk += 2) {
                 const int col0 = n_tile * BLOCK_N + chunk * 32;
-                if (col0 >= p.N) break;         // uniform across the CTA
+                if (col0 >= p.N) break;         // uniform across the group
                 uint32_t v[32];
                 tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BLOCK_N + chunk * 32), v);
                 tmem_ld_wait();
-                const float *arow = (p.addend && row_ok) ? p.addend + row * p.ld_addend + col0 : nullptr;
                 const bool full_cols = col0 + 32 <= p.N;
-                // affine part: folded batch-norm scale/shift + bias, optional addend
+                // affine part: folded batch-norm scale/shift + bias (vectors padded to a multiple of 32)
+                if (p.scale) {
 #pragma unroll
-                for (int j = 0; j < 32; j++) {
-                    float x = __uint_as_float(v[j]);
-                    const int c = full_cols ? col0 + j : min(col0 + j, p.N - 1);
-                    if (p.scale) x *= __ldg(p.scale + c);
-                    if (p.shift) x += __ldg(p.shift + c);
-                    if (arow && (full_cols || col0 + j < p.N)) x += arow[j];
-                    v[j] = __float_as_uint(x);
+                    for (int j = 0; j < 32; j += 4) {
+                        const float4 sc = __ldg(reinterpret_cast<const float4 *>(p.scale + col0 + j));
+                        const float4 sh = __ldg(reinterpret_cast<const float4 *>(p.shift + col0 + j));
+                        v[j] = __float_as_uint(fmaf(__uint_as_float(v[j]), sc.x, sh.x));
+                        v[j + 1] = __float_as_uint(fmaf(__uint_as_float(v[j + 1]), sc.y, sh.y));
+                        v[j + 2] = __float_as_uint(fmaf(__uint_as_float(v[j + 2]), sc.z, sh.z));
+                        v[j + 3] = __float_as_uint(fmaf(__uint_as_float(v[j + 3]), sc.w, sh.w));
+                    }
+                } else if (p.shift) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) {
+                        const float4 sh = __ldg(reinterpret_cast<const float4 *>(p.shift + col0 + j));
+                        v[j] = __float_as_uint(__uint_as_float(v[j]) + sh.x);
+                        v[j + 1] = __float_as_uint(__uint_as_float(v[j + 1]) + sh.y);
+                        v[j + 2] = __float_as_uint(__uint_as_float(v[j + 2]) + sh.z);
+                        v[j + 3] = __float_as_uint(__uint_as_float(v[j + 3]) + sh.w);
+                    }
+                }
+                if (p.addend && row_ok) {
+                    const float *arow = p.addend + row * p.ld_addend + col0;
+                    if (full_cols && p.addend_vec) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            const float4 ad = *reinterpret_cast<const float4 *>(arow + j);
+                            v[j] = __float_as_uint(__uint_as_float(v[j]) + ad.x);
+                            v[j + 1] = __float_as_uint(__uint_as_float(v[j + 1]) + ad.y);
+                            v[j + 2] = __float_as_uint(__uint_as_float(v[j + 2]) + ad.z);
+                            v[j + 3] = __float_as_uint(__uint_as_float(v[j + 3]) + ad.w);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j++)
+                            if (col0 + j < p.N) v[j] = __float_as_uint(__uint_as_float(v[j]) + arow[j]);
+                    }
                 }
                 // activation: the common ones inline, the rest through one out-of-line call per value
                 if (p.act == NB_ACT_RELU) {
@@ -404,61 +448,59 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
 #pragma unroll
                     for (int j = 0; j < 32; j++) v[j] = __float_as_uint(round_tf32(__uint_as_float(v[j])));
                 }
-                if (p.pool) {
-                    // conv + 2x2/2 max-pool (pooling_layer.cc:117-146): the full-resolution slab stays in
-                    // shared memory (buffer 0); each thread reduces two 16-byte chunks of one pooled pixel
-                    // into one of two small pooled buffers (inside buffer 1), which leaves by TMA.
-                    float4 *slab0 = reinterpret_cast<float4 *>(out_stage);
-                    float4 *pooled = reinterpret_cast<float4 *>(out_stage + C::OUT_STAGE_BYTES + slab * 4096);
-                    if (store_thread) tma_store_wait_read<1>();
-                    epilogue_bar_sync();
-#pragma unroll
-                    for (int j = 0; j < 8; j++)
-                        slab0[r * 8 + (j ^ (r & 7))] = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
-                                                                  __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
-                    epilogue_bar_sync();
-                    const int t = threadIdx.x - 64;
-                    const int pr = t >> 2, hw = p.bw >> 1, hh = p.bh >> 1;
-                    const int pw = pr % hw, ph = (pr / hw) % hh, pn = pr / (hw * hh);
-                    if (pn < p.bn) {
-                        const int r00 = (pn * p.bh + 2 * ph) * p.bw + 2 * pw;
-#pragma unroll
-                        for (int e = 0; e < 2; e++) {
-                            const int c = (t & 3) * 2 + e;
-                            float4 m = make_float4(-1e8f, -1e8f, -1e8f, -1e8f);     // the reference's identity
-#pragma unroll
-                            for (int w4 = 0; w4 < 4; w4++) {
-                                const int rr = r00 + (w4 >> 1) * p.bw + (w4 & 1);
-                                const float4 x4 = slab0[rr * 8 + (c ^ (rr & 7))];
-                                m.x = x4.x > m.x ? x4.x : m.x; m.y = x4.y > m.y ? x4.y : m.y;
-                                m.z = x4.z > m.z ? x4.z : m.z; m.w = x4.w > m.w ? x4.w : m.w;
-                            }
-                            pooled[pr * 8 + (c ^ (pr & 7))] = m;
-                        }
-                    }
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    epilogue_bar_sync();
-                    if (store_thread) {
-                        tma_store_4d(&p.tm_yp, pooled, col0, tw * hw, th * hh, tn * p.bn);
-                        tma_store_commit();
-                    }
-                    slab ^= 1;
-                } else if (p.tma_store) {
-                    // the store issued two slabs ago must have finished reading this buffer
-                    if (store_thread) tma_store_wait_read<1>();
-                    epilogue_bar_sync();
-                    float4 *dst = reinterpret_cast<float4 *>(out_stage + slab * C::OUT_STAGE_BYTES + r * 128);
+                if (p.pool || p.tma_store) {
+                    // the group's previous store must have finished reading the staging buffer
+                    if (store_thread) tma_store_wait_read<0>();
+                    epilogue_bar_sync(bar_id);
 #pragma unroll
                     for (int j = 0; j < 8; j++)     // 16-byte chunk j of row r lives at chunk j ^ (r % 8)
-                        dst[j ^ (r & 7)] = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
-                                                       __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    epilogue_bar_sync();
-                    if (store_thread) {
-                        tma_store_4d(&p.tm_y, out_stage + slab * C::OUT_STAGE_BYTES, col0, tw * p.bw, th * p.bh, tn * p.bn);
-                        tma_store_commit();
+                        slab[r * 8 + (j ^ (r & 7))] = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                                                 __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+                    if (!p.pool) {
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        epilogue_bar_sync(bar_id);
+                        if (store_thread) {
+                            tma_store_4d(&p.tm_y, slab, col0, tw * p.bw, th * p.bh, tn * p.bn);
+                            tma_store_commit();
+                        }
+                    } else {
+                        // conv + 2x2/2 max-pool (pooling_layer.cc:117-146): each thread reduces two 16-byte
+                        // chunks of one pooled pixel from the full-resolution slab, then the pooled rows
+                        // overwrite the head of the same buffer and leave by TMA.
+                        epilogue_bar_sync(bar_id);
+                        const int pr = t >> 2, hw = p.bw >> 1, hh = p.bh >> 1;
+                        const int pw = pr % hw, ph = (pr / hw) % hh, pn = pr / (hw * hh);
+                        float4 m[2];
+                        if (pn < p.bn) {
+                            const int r00 = (pn * p.bh + 2 * ph) * p.bw + 2 * pw;
+#pragma unroll
+                            for (int e = 0; e < 2; e++) {
+                                const int c = (t & 3) * 2 + e;
+                                m[e] = make_float4(-1e8f, -1e8f, -1e8f, -1e8f);     // the reference's identity
+#pragma unroll
+                                for (int w4 = 0; w4 < 4; w4++) {
+                                    const int rr = r00 + (w4 >> 1) * p.bw + (w4 & 1);
+                                    const float4 x4 = slab[rr * 8 + (c ^ (rr & 7))];
+                                    m[e].x = x4.x > m[e].x ? x4.x : m[e].x; m[e].y = x4.y > m[e].y ? x4.y : m[e].y;
+                                    m[e].z = x4.z > m[e].z ? x4.z : m[e].z; m[e].w = x4.w > m[e].w ? x4.w : m[e].w;
+                                }
+                            }
+                        }
+                        epilogue_bar_sync(bar_id);      // every source row has been read
+                        if (pn < p.bn) {
+#pragma unroll
+                            for (int e = 0; e < 2; e++) {
+                                const int c = (t & 3) * 2 + e;
+                                slab[pr * 8 + (c ^ (pr & 7))] = m[e];
+                            }
+                        }
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        epilogue_bar_sync(bar_id);
+                        if (store_thread) {
+                            tma_store_4d(&p.tm_yp, slab, col0, tw * hw, th * hh, tn * p.bn);
+                            tma_store_commit();
+                        }
                     }
-                    slab ^= 1;
                 } else if (row_ok) {
                     float *yrow = p.y + row * p.ldy + col0;
 #pragma unroll
@@ -471,12 +513,62 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
             if (++acc == 2) { acc = 0; acc_phase ^= 1; }
         }
         if (store_thread) tma_store_wait_all();     // staged tiles must have left shared memory
+    } else if (p.gather) {
+        // ------------------------------------------------- in-kernel patch gather
+        // One thread per tile row (output pixel): 32 columns (kh,kw,c) of this K block are read
+        // through the cache (neighbouring threads read neighbouring pixels) and written as one
+        // 128-byte swizzled row, TF32-rounded (or split into hi/lo for the three-pass kernel).
+        const int t = threadIdx.x - 320;
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            const int m_tile = tile / p.n_tiles;
+            const long m = (long)m_tile * BLOCK_M + t;
+            const bool valid = m < p.gM;
+            int ih0 = 0, iw0 = 0;
+            const float *base = p.gx;
+            if (valid) {
+                const int per = p.gOH * p.gOW;
+                const int n = (int)(m / per), rem = (int)(m - (long)n * per);
+                const int oh = rem / p.gOW, ow = rem - oh * p.gOW;
+                ih0 = oh * p.gstride; iw0 = ow * p.gstride;
+                base = p.gx + (long)n * p.gsn + (long)ih0 * p.gsh + (long)iw0 * p.gsw;
+            }
+            for (int kb = 0; kb < p.num_k_blocks; kb++) {
+                if (!(ok = mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status))) break;
+                float4 *a_row = reinterpret_cast<float4 *>(smem + stage * C::STAGE_BYTES + t * 128);
+                float4 *a_lo_row = reinterpret_cast<float4 *>(smem + stage * C::STAGE_BYTES + A_STAGE_BYTES + C::B_STAGE_BYTES + t * 128);
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    float v[4], lo[4];
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        const int2 tb = __ldg(p.gtab + kb * BLOCK_K + j * 4 + e);
+                        const int ih = ih0 + (int)(short)(tb.y & 0xffff), iw = iw0 + (tb.y >> 16);
+                        float x = 0.0f;
+                        if (valid && ih >= 0 && ih < p.gH && iw >= 0 && iw < p.gW) x = __ldg(base + tb.x);
+                        if (THREE) {
+                            v[e] = __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
+                            lo[e] = x - v[e];
+                        } else {
+                            v[e] = p.ground ? round_tf32(x) : x;
+                        }
+                    }
+                    a_row[j ^ (t & 7)] = make_float4(v[0], v[1], v[2], v[3]);
+                    if (THREE) a_lo_row[j ^ (t & 7)] = make_float4(lo[0], lo[1], lo[2], lo[3]);
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                mbar_arrive(&full[stage]);
+                if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            }
+        }
     } else if (THREE) {
         // ---------------------------------------------- hi/lo operand splitter
         // hi = the TF32 the tensor core would read (low 13 mantissa bits cleared),
         // lo = x - hi (exact in fp32).  Element positions are kept, so the swizzled
         // tile layout written by TMA is preserved.
-        const int t = threadIdx.x - 192;        // 0..127
+        const int t = threadIdx.x - 320;        // 0..127
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
@@ -563,7 +655,8 @@ void launch(nb_handle_s *h, const TcParams &p) {
     }
     const int tiles = p.m_tiles * p.n_tiles;
     const int grid = std::max(1, std::min(tiles, h->sm_count));
-    kern<<<grid, C::THREADS, C::SMEM_BYTES, h->stream>>>(p);
+    const int threads = (THREE || p.gather) ? 448 : 320;
+    kern<<<grid, threads, C::SMEM_BYTES, h->stream>>>(p);
     check_launch("gemm_tf32_tcgen05_kernel");
     count_launch(h);
 }
@@ -574,6 +667,7 @@ inline bool aligned16(const void *p) { return ((uintptr_t)p & 15) == 0; }
 
 bool gemm_tc_supported(const nb_handle_s *h, const GemmArgs &a) {
     if (!h->encode_tiled || h->cc_major != 10) return false;
+    if (a.gather_table) return (a.Kc % 32) == 0 && (a.ldb % 4) == 0 && aligned16(a.b);
     if (a.Kc < 32 || (a.Kc % 4) != 0 || (a.ldb % 4) != 0 || !aligned16(a.b) || !aligned16(a.a)) return false;
     if (a.a_is_conv) {
         const ConvGeom &g = a.g;
@@ -588,12 +682,14 @@ bool gemm_tc_supported(const nb_handle_s *h, const GemmArgs &a) {
 
 void gemm_tc(nb_handle_s *h, const GemmArgs &a, bool three_pass) {
     if (!gemm_tc_supported(h, a)) throw Error(NB_ERR_UNSUPPORTED, "operands do not satisfy the TMA layout rules");
+    if (a.y_pool && a.gather_table) throw Error(NB_ERR_UNSUPPORTED, "fused pooling is not available with the gathered A operand");
     if (three_pass && !a.b_lo) throw Error(NB_ERR_INVALID_ARG, "three-pass GEMM needs the low-order weight split");
     TcParams p;
     std::memset(&p, 0, sizeof p);
 
     ConvGeom g;
-    if (a.a_is_conv) {
+    const bool gather = a.gather_table != nullptr;
+    if (a.a_is_conv && !gather) {
         g = a.g;
     } else {
         // plain matrix = one image of height 1 and width M with Kc channels, 1x1 filter
@@ -617,6 +713,7 @@ void gemm_tc(nb_handle_s *h, const GemmArgs &a, bool three_pass) {
     p.tx_bytes_a = BLOCK_K * 4 * box.bw * box.bh * box.bn;
     p.scale = a.scale; p.shift = a.shift; p.addend = a.addend; p.ld_addend = a.ld_addend;
     p.act = a.act; p.round_out = a.round_out_tf32 ? 1 : 0;
+    p.addend_vec = a.addend && aligned16(a.addend) && (a.ld_addend % 4) == 0;
     p.y = a.y; p.ldy = a.ldy;
     p.tma_store = a.y && aligned16(a.y) && (a.ldy % 4) == 0;
     p.pool = pool ? 1 : 0;
@@ -640,7 +737,14 @@ void gemm_tc(nb_handle_s *h, const GemmArgs &a, bool three_pass) {
     }
     p.n_tiles = (a.N + block_n - 1) / block_n;
 
-    {   // A: dims {C, W, H, N}
+    p.gather = gather ? 1 : 0;
+    if (gather) {
+        p.gx = a.a; p.gtab = (const int2 *)a.gather_table;
+        p.gsn = a.g.sn; p.gsh = a.g.sh; p.gsw = a.g.sw;
+        p.gH = a.g.H; p.gW = a.g.W; p.gOH = a.g.OH; p.gOW = a.g.OW; p.gstride = a.g.stride; p.gM = a.M;
+        p.ground = three_pass ? 0 : 1;
+    }
+    if (!gather) {   // A: dims {C, W, H, N}
         cuuint64_t dims[4] = {(cuuint64_t)a.Kc, (cuuint64_t)g.W, (cuuint64_t)g.H, (cuuint64_t)g.batch};
         cuuint64_t strides[3] = {(cuuint64_t)g.sw * 4, (cuuint64_t)g.sh * 4, (cuuint64_t)g.sn * 4};
         cuuint32_t bx[4] = {(cuuint32_t)BLOCK_K, (cuuint32_t)(box.bw * g.stride), (cuuint32_t)(box.bh * g.stride),

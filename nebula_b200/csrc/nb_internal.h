@@ -99,6 +99,11 @@ struct GemmArgs {
     bool a_is_conv = false;     // false: plain [M,K] with row stride lda
     long lda = 0;
     ConvGeom g;                 // used when a_is_conv
+    // tensor-core path only: build A in shared memory from the strided tensor described by g instead
+    // of loading it by TMA.  Entry kk of the table (Kc entries, Kc % 32 == 0) is
+    // {element offset of (c, kh-pad, kw-pad), ((kh-pad) & 0xffff) | (kw-pad) << 16}; the B operand is then
+    // a plain [N][Kc] matrix.
+    const void *gather_table = nullptr;
     // B operand: [taps][N][Kc] (taps = ksize*ksize, Kc = channels per tap, row stride ldb)
     const float *b = nullptr;       // operand used by the TF32 / FP32 paths
     const float *b_lo = nullptr;    // low-order split of B for the 3xTF32 path
@@ -146,8 +151,7 @@ void launch_shortcut(nb_handle_s *h, const nb_shortcut_desc_t &d, const float *p
                      bool round_tf32);
 // weights OIHW [F,C,k,k] -> [k*k][F][Cp] (Cp >= C, zero padded), optionally permuting FC columns
 void launch_weight_relayout(nb_handle_s *h, const float *w_oihw, float *dst, int F, int C, int k, int Cp);
-// explicit patch matrix [pixels][Kpad] (column = (kh,kw,c)) and the matching weight layout [F][Kpad]
-void launch_pack_patches(nb_handle_s *h, const float *x, float *out, const ConvGeom &g, int Kpad, bool round_tf32);
+// weights OIHW -> [F][Kpad] with column (kh,kw,c), zero padded: the B operand of the gathered-A convolution
 void launch_weight_pack(nb_handle_s *h, const float *w_oihw, float *dst, int F, int C, int k, int Kpad);
 // FC weights whose columns index (c,h,w) -> columns indexing (h,w,c)
 void launch_fc_permute(nb_handle_s *h, const float *w, float *dst, int out, int C, int H, int W);

@@ -18,6 +18,11 @@ void upload(nb_handle_s *h, DeviceBuffer &dst, const float *src, size_t n, int m
 void upload_vec(nb_handle_s *h, DeviceBuffer &dst, const std::vector<float> &v) {
     upload(h, dst, v.data(), v.size(), NB_MEM_HOST);
 }
+// Per-column epilogue vectors are read 32 columns at a time: pad them to a multiple of 32.
+void upload_padded(nb_handle_s *h, DeviceBuffer &dst, std::vector<float> v, float fill) {
+    v.resize((v.size() + 31) / 32 * 32, fill);
+    upload_vec(h, dst, v);
+}
 std::vector<float> to_host(nb_handle_s *h, const float *src, size_t n, int mem) {
     std::vector<float> v(n);
     if (!n) return v;
@@ -87,8 +92,8 @@ void ConvPlan::set_weights(const float *weight, const float *bias, const float *
     }
     fold_bn(d.filters, hb.data(), hg.data(), hm.data(), hv.data(), d.batch_normalize != 0, sc, sh);
     has_scale = !sc.empty();
-    if (has_scale) upload_vec(h, scale, sc);
-    upload_vec(h, shift, sh);
+    if (has_scale) upload_padded(h, scale, sc, 1.0f);
+    upload_padded(h, shift, sh, 0.0f);
     ready = true;
 }
 
@@ -118,7 +123,7 @@ void ConvPlan::forward(const float *x, float *y, const ForwardOpts &o) {
     g.ksize = d.size; g.stride = d.stride; g.pad = d.padding;
 
     if (pth == PATH_SIMT && pack_ok && h->math_mode != NB_MATH_FP32 && h->encode_tiled) {
-        // tensor-core route for small channel counts: pack patches, then a plain GEMM
+        // tensor-core route for small channel counts: the kernel gathers the patches itself
         const bool three = h->math_mode == NB_MATH_TF32X3;
         const size_t M = (size_t)d.batch * OH * OW;
         if (o.x_nhwc) {
@@ -126,10 +131,28 @@ void ConvPlan::forward(const float *x, float *y, const ForwardOpts &o) {
         } else {
             g.sw = 1; g.sh = d.width; g.sc = (long)d.height * d.width; g.sn = (long)d.channels * d.height * d.width;
         }
-        if (x_scratch.n < M * Kpad) x_scratch.alloc(M * Kpad);
-        launch_pack_patches(h, x, x_scratch.p, g, Kpad, !three);
+        // column kk = (kh,kw,c) -> where to read it, relative to the pixel's origin (oh*stride, ow*stride)
+        DeviceBuffer &tab = gather_tab[o.x_nhwc ? 1 : 0];
+        if (!tab.p) {
+            std::vector<int> host((size_t)2 * Kpad);
+            const int K = d.channels * d.size * d.size;
+            for (int kk = 0; kk < Kpad; kk++) {
+                int off = 0, dh = 30000, dw = 0;        // padding columns: a row offset that is never inside the image
+                if (kk < K) {
+                    const int tap = kk / d.channels, c = kk - tap * d.channels;
+                    dh = tap / d.size - d.padding; dw = tap % d.size - d.padding;
+                    off = (int)(c * g.sc + dh * g.sh + dw * g.sw);
+                }
+                host[2 * kk] = off;
+                host[2 * kk + 1] = (dh & 0xffff) | (dw << 16);
+            }
+            tab.alloc((size_t)2 * Kpad);
+            NB_CHECK_CUDA(cudaMemcpyAsync(tab.p, host.data(), host.size() * sizeof(int), cudaMemcpyHostToDevice, h->stream));
+            NB_CHECK_CUDA(cudaStreamSynchronize(h->stream));
+        }
         GemmArgs pa;
-        pa.a = x_scratch.p; pa.lda = Kpad; pa.ldb = Kpad; pa.M = (int)M; pa.N = d.filters; pa.Kc = Kpad;
+        pa.a = x; pa.a_is_conv = true; pa.g = g; pa.gather_table = tab.p;
+        pa.ldb = Kpad; pa.M = (int)M; pa.N = d.filters; pa.Kc = Kpad;
         pa.scale = has_scale ? scale.p : nullptr; pa.shift = shift.p; pa.act = d.activation;
         pa.round_out_tf32 = o.round_out; pa.addend = o.addend; pa.ld_addend = d.filters;
         float *yo = y;
@@ -233,8 +256,8 @@ void FcPlan::set_weights(const float *weight, const float *bias, const float *g,
     }
     fold_bn(d.outputs, hb.data(), hg.data(), hm.data(), hv.data(), d.batch_normalize != 0, sc, sh);
     has_scale = !sc.empty();
-    if (has_scale) upload_vec(h, scale, sc);
-    upload_vec(h, shift, sh);
+    if (has_scale) upload_padded(h, scale, sc, 1.0f);
+    upload_padded(h, shift, sh, 0.0f);
     ready = true;
 }
 
@@ -334,7 +357,7 @@ void LstmPlan::set_weights(const float *stream, size_t count, int mem) {
     upload_vec(h, wu.exact, u);
     upload_vec(h, ww.exact, wr);
     wu.split_ready = ww.split_ready = false;
-    upload_vec(h, shift, sh);
+    upload_padded(h, shift, sh, 0.0f);
     ready = true;
 }
 

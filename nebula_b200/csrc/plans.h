@@ -54,10 +54,11 @@ struct ConvPlan : nb_plan_s {
     int OH, OW, Cp;
     WeightSet w;                    // [tap][F][Cp]
     // Small channel counts (3-channel input layers) cannot be addressed by TMA boxes:
-    // their patches are packed into an explicit [pixels][Kpad] matrix instead.
+    // the kernel's gather warps build those A tiles in shared memory instead.
     bool pack_ok = false;
     int Kpad = 0;
     WeightSet wp;                   // [F][Kpad], column = (kh,kw,c)
+    DeviceBuffer gather_tab[2];     // column -> input offset table for NCHW [0] and NHWC [1] inputs
     DeviceBuffer scale, shift;
     bool has_scale = false, ready = false;
     DeviceBuffer x_scratch, y_scratch;
@@ -107,6 +108,7 @@ struct LstmPlan : nb_plan_s {
 // host or device source -> freshly filled device buffer
 void upload(nb_handle_s *h, DeviceBuffer &dst, const float *src, size_t n, int mem);
 void upload_vec(nb_handle_s *h, DeviceBuffer &dst, const std::vector<float> &v);
+void upload_padded(nb_handle_s *h, DeviceBuffer &dst, std::vector<float> v, float fill);
 std::vector<float> to_host(nb_handle_s *h, const float *src, size_t n, int mem);
 
 }  // namespace nb

@@ -68,8 +68,10 @@ extern "C" int nb_fc_forward_static(nb_handle_t h, const float *x, const float *
         const bool tensor_core = h->math_mode != NB_MATH_FP32 && h->encode_tiled && (inputs % 4) == 0 && inputs >= 32 &&
                                  aligned16(x) && aligned16(weight) && aligned16(y);
         const bool three = h->math_mode == NB_MATH_TF32X3;
-        // working copies: TF32 -> rounded x and rounded W; 3xTF32 -> hi and lo parts of W
-        const size_t need = !tensor_core ? 0 : (three ? 2 * round_up64(wn) : round_up64(xn) + round_up64(wn));
+        // working copies: TF32 -> rounded x and rounded W; 3xTF32 -> hi and lo parts of W; plus the bias,
+        // which the kernel reads 32 columns at a time (the copy is padded to a multiple of 64)
+        const size_t bn = round_up64((size_t)outputs);
+        const size_t need = !tensor_core ? 0 : bn + (three ? 2 * round_up64(wn) : round_up64(xn) + round_up64(wn));
         if (need > NB_STATIC_SCRATCH_FLOATS)
             throw nb::Error(NB_ERR_INVALID_ARG,
                             "connected (static): needs " + std::to_string(need) + " scratch floats, the built-in array holds " +
@@ -85,6 +87,9 @@ extern "C" int nb_fc_forward_static(nb_handle_t h, const float *x, const float *
             nb::gemm_simt(h, a);
         } else {
             float *scratch = scratch_for_device(h->device);
+            NB_CHECK_CUDA(cudaMemcpyAsync(scratch, bias, (size_t)outputs * sizeof(float), cudaMemcpyDeviceToDevice, h->stream));
+            a.shift = scratch;          // columns beyond `outputs` hold stale values that only masked lanes see
+            scratch += bn;
             if (three) {
                 float *w_hi = scratch, *w_lo = scratch + round_up64(wn);
                 nb::launch_split_tf32(h, weight, w_hi, w_lo, wn);
