@@ -82,6 +82,8 @@ typedef struct {
     unsigned long long tc_launches;
     double simt_ms, simt_flops;
     unsigned long long simt_launches;
+    double halo_ms, halo_flops;             /* the 3x3 halo convolution kernel (few input channels) */
+    unsigned long long halo_launches;
 } nb_profile_t;
 int nb_profile_begin(nb_handle_t handle);
 int nb_profile_end(nb_handle_t handle, nb_profile_t *result);

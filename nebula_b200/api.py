@@ -55,7 +55,8 @@ class LstmDesc(C.Structure):
 
 class Profile(C.Structure):
     _fields_ = [("tc_ms", C.c_double), ("tc_flops", C.c_double), ("tc_launches", C.c_ulonglong),
-                ("simt_ms", C.c_double), ("simt_flops", C.c_double), ("simt_launches", C.c_ulonglong)]
+                ("simt_ms", C.c_double), ("simt_flops", C.c_double), ("simt_launches", C.c_ulonglong),
+                ("halo_ms", C.c_double), ("halo_flops", C.c_double), ("halo_launches", C.c_ulonglong)]
 
 
 class LayerInfo(C.Structure):

@@ -148,6 +148,7 @@ int nb_profile_end(nb_handle_t h, nb_profile_t *r) {
             float ms = 0;
             NB_CHECK_CUDA(cudaEventElapsedTime(&ms, t.start, t.stop));
             if (t.kind == 0) { r->tc_ms += ms; r->tc_flops += t.flops; r->tc_launches++; }
+            else if (t.kind == 2) { r->halo_ms += ms; r->halo_flops += t.flops; r->halo_launches++; }
             else { r->simt_ms += ms; r->simt_flops += t.flops; r->simt_launches++; }
             cudaEventDestroy(t.start); cudaEventDestroy(t.stop);
         }

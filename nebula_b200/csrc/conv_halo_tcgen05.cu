@@ -1,0 +1,316 @@
+// 3x3 stride-1 convolution for layers with few input channels (C <= 128), where the
+// generic implicit-GEMM kernel is bound by L2 -> shared-memory traffic: it re-loads
+// the activation tile once per filter tap (9x the input bytes).
+//
+// Here every 32-channel slice of the input is loaded ONCE per tile as a halo box
+// {32 ch, bw+2, bh+2} and all nine taps read it in place: tap (kh,kw) is the same
+// shared-memory tile with the operand descriptor's start address advanced by
+// (kh*(bw+2) + kw) rows of 128 bytes (the 128-byte swizzle is a function of the
+// shared-memory address, so a row-shifted start stays consistent with what TMA
+// wrote).  The accumulator rows therefore run over a (bw+2)-wide raster: two
+// columns per image row are junk and are dropped by the epilogue when it compacts
+// rows into the staging slab.  A tile is 1 or 2 such 128-row halves (two MMAs per
+// K step share one weight tile, halving the weight traffic per pixel); weights are
+// streamed per tap through their own ring.
+//
+// Replaces the same reference code as the generic kernel
+// (models/layers/convolutional_layer.cu:47-70, common/utils.cu:34-74) for these
+// layers; same fused epilogue (batch-norm/bias/activation/TF32 rounding, optional
+// 2x2/2 max-pool).  Warp roles: 0 TMA producer, 1 MMA issuer, 2-9 epilogue.
+// Every wait is bounded, as in the generic kernel.
+#include <algorithm>
+#include <cstring>
+
+#include "tc_common.cuh"
+
+namespace nb {
+
+using namespace tc;
+
+namespace {
+
+constexpr int A_RING = 3;
+constexpr int A_BYTES = 37 * 1024;          // up to 296 rows of 128 B: halo box + slack for the last tap's overrun
+constexpr int OUT_BYTES = BLOCK_M * 32 * 4;
+
+struct HaloParams {
+    CUtensorMap tm_a, tm_b, tm_y, tm_yp;
+    int bw, bh, wt;             // valid tile width/height in pixels, raster width wt = bw + 2
+    int halves;                 // 128-row accumulator halves per tile (1 or 2)
+    int rows_half;              // image rows per half (128 / wt when halves == 2, else bh)
+    int tiles_w, tiles_h, NB, OW, OH;
+    int pad;
+    int c_blocks;
+    int m_tiles, n_tiles;
+    int halo_bytes;
+    EpiParams e;
+    int *status;
+};
+
+template <int BLOCK_N>
+struct HCfg {
+    static constexpr int B_BYTES = BLOCK_N * BLOCK_K * 4;
+    static constexpr int B_RING = 64 * 1024 / B_BYTES;                // 8 (N=64) or 4 (N=128)
+    static constexpr int SMEM_BYTES = A_RING * A_BYTES + B_RING * B_BYTES + 2 * OUT_BYTES + 1024 + 256;
+};
+
+template <int BLOCK_N>
+__global__ void __launch_bounds__(320, 1) conv3x3_halo_tcgen05_kernel(const __grid_constant__ HaloParams p) {
+    using C = HCfg<BLOCK_N>;
+    constexpr int B_RING = C::B_RING;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t *a_ring = smem;
+    uint8_t *b_ring = a_ring + A_RING * A_BYTES;
+    uint8_t *out_stage = b_ring + B_RING * C::B_BYTES;
+    uint64_t *bars = (uint64_t *)(out_stage + 2 * OUT_BYTES);
+    uint64_t *a_full = bars, *a_empty = a_full + A_RING;
+    uint64_t *b_full = a_empty + A_RING, *b_empty = b_full + B_RING;
+    uint64_t *acc_full = b_empty + B_RING, *acc_empty = acc_full + 2;
+    uint32_t *tmem_slot = (uint32_t *)(acc_empty + 2);
+    volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int total_tiles = p.m_tiles * p.n_tiles;
+    const int acc_cols = p.halves * BLOCK_N;            // TMEM columns of one accumulator set
+    // power of two >= 2 * acc_cols
+    const uint32_t tmem_cols = (2 * acc_cols <= 128) ? 128 : (2 * acc_cols <= 256 ? 256 : 512);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < A_RING; s++) { mbar_init(&a_full[s], 1); mbar_init(&a_empty[s], 1); }
+        for (int s = 0; s < B_RING; s++) { mbar_init(&b_full[s], 1); mbar_init(&b_empty[s], 1); }
+        for (int a = 0; a < 2; a++) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 256); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(tmem_cols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------ TMA producer
+        if (elect_one()) {
+            int sa = 0, sb = 0;
+            uint32_t pa = 0, pb = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int m_tile = tile / p.n_tiles, n_tile = tile % p.n_tiles;
+                const int tw = m_tile % p.tiles_w;
+                const int th = (m_tile / p.tiles_w) % p.tiles_h;
+                const int n = m_tile / (p.tiles_w * p.tiles_h);
+                for (int cb = 0; cb < p.c_blocks && ok; cb++) {
+                    if (!(ok = mbar_wait(&a_empty[sa], pa ^ 1, abort_flag, p.status))) break;
+                    mbar_expect_tx(&a_full[sa], (uint32_t)p.halo_bytes);
+                    tma_load_4d(a_ring + sa * A_BYTES, &p.tm_a, &a_full[sa], cb * BLOCK_K, tw * p.bw - p.pad,
+                                th * p.bh - p.pad, n);
+                    if (++sa == A_RING) { sa = 0; pa ^= 1; }
+                    for (int tap = 0; tap < 9; tap++) {
+                        if (!(ok = mbar_wait(&b_empty[sb], pb ^ 1, abort_flag, p.status))) break;
+                        mbar_expect_tx(&b_full[sb], (uint32_t)C::B_BYTES);
+                        tma_load_3d(b_ring + sb * C::B_BYTES, &p.tm_b, &b_full[sb], cb * BLOCK_K, n_tile * BLOCK_N, tap);
+                        if (++sb == B_RING) { sb = 0; pb ^= 1; }
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // -------------------------------------------------------- MMA issuer
+        if (elect_one()) {
+            constexpr uint32_t idesc = make_idesc(BLOCK_M, BLOCK_N);
+            int sa = 0, sb = 0, acc = 0;
+            uint32_t pa = 0, pb = 0, acc_phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                if (!(ok = mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag, p.status))) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * acc_cols);
+                for (int cb = 0; cb < p.c_blocks && ok; cb++) {
+                    if (!(ok = mbar_wait(&a_full[sa], pa, abort_flag, p.status))) break;
+                    tc_fence_after();
+                    const uint32_t a_base = smem_u32(a_ring + sa * A_BYTES);
+                    for (int tap = 0; tap < 9; tap++) {
+                        if (!(ok = mbar_wait(&b_full[sb], pb, abort_flag, p.status))) break;
+                        tc_fence_after();
+                        const uint32_t b_base = smem_u32(b_ring + sb * C::B_BYTES);
+                        const int kh = tap / 3, kw = tap - kh * 3;
+                        const uint32_t a_tap = a_base + (uint32_t)((kh * p.wt + kw) * 128);
+                        for (int hf = 0; hf < p.halves; hf++) {
+#pragma unroll
+                            for (int k = 0; k < BLOCK_K / UMMA_K; k++) {
+                                const uint32_t koff = k * UMMA_K * 4;
+                                umma_tf32(d_tmem + (uint32_t)(hf * BLOCK_N), make_smem_desc(a_tap + hf * (BLOCK_M * 128) + koff),
+                                          make_smem_desc(b_base + koff), idesc, (cb | tap | k) != 0);
+                            }
+                        }
+                        umma_commit(&b_empty[sb]);
+                        if (++sb == B_RING) { sb = 0; pb ^= 1; }
+                    }
+                    if (ok) umma_commit(&a_empty[sa]);
+                    if (++sa == A_RING) { sa = 0; pa ^= 1; }
+                }
+                if (ok) umma_commit(&acc_full[acc]);
+                if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+            }
+        }
+        __syncwarp();
+    } else {
+        // ---------------------------------------------------------- epilogue
+        const int ew = warp - 2, grp = ew >> 2, bar_id = 1 + grp;
+        const int q = warp & 3;
+        const int r = q * 32 + lane;
+        const int t = (ew & 3) * 32 + lane;
+        const bool store_thread = t == 0;
+        float4 *slab = reinterpret_cast<float4 *>(out_stage + grp * OUT_BYTES);
+        const int chunks_n = BLOCK_N / 32;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            const int m_tile = tile / p.n_tiles, n_tile = tile % p.n_tiles;
+            const int tw = m_tile % p.tiles_w;
+            const int th = (m_tile / p.tiles_w) % p.tiles_h;
+            const int n = m_tile / (p.tiles_w * p.tiles_h);
+            if (!(ok = epilogue_all(mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status), bar_id))) break;
+            tc_fence_after();
+#pragma unroll 1
+            for (int item = grp; item < p.halves * chunks_n; item += 2) {
+                const int hf = item / chunks_n, chunk = item - hf * chunks_n;
+                const int col0 = n_tile * BLOCK_N + chunk * 32;
+                if (col0 >= p.e.N) continue;        // uniform across the group
+                // accumulator row -> raster position -> pixel of this half's box
+                const int m = hf * BLOCK_M + r;
+                const int jh = m / p.wt, jw = m - jh * p.wt;
+                const int lh = jh - hf * p.rows_half;                  // row inside the half's box
+                const bool in_box = jw < p.bw && jh < p.bh && lh >= 0 && lh < p.rows_half;
+                const int ow = tw * p.bw + jw, oh = th * p.bh + jh;
+                EpiRow rw;
+                rw.srow = in_box ? lh * p.bw + jw : -1;
+                rw.row_ok = in_box && ow < p.OW && oh < p.OH;
+                rw.grow = ((long)n * p.OH + oh) * p.OW + ow;
+                const EpiBox bx{p.bw, p.rows_half, 1, tw * p.bw, th * p.bh + hf * p.rows_half, n};
+                uint32_t v[32];
+                tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * acc_cols + hf * BLOCK_N + chunk * 32), v);
+                tmem_ld_wait();
+                epilogue_chunk(p.e, &p.tm_y, &p.tm_yp, v, col0, rw, bx, slab, bar_id, store_thread, t);
+            }
+            tc_fence_before();
+            mbar_arrive(&acc_empty[acc]);
+            if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        }
+        if (store_thread) tma_store_wait_all();
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        for (int i = 0; i < 64; i++) __nanosleep(2000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+    }
+}
+
+void encode(nb_handle_s *h, CUtensorMap *tm, const void *base, int rank, const cuuint64_t *dims,
+            const cuuint64_t *strides_bytes, const cuuint32_t *box) {
+    cuuint32_t es[5] = {1, 1, 1, 1, 1};
+    CUresult r = h->encode_tiled(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, const_cast<void *>(base), dims,
+                                 strides_bytes, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                 CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) throw Error(NB_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+}
+
+template <int BLOCK_N>
+void launch(nb_handle_s *h, const HaloParams &p) {
+    auto kern = conv3x3_halo_tcgen05_kernel<BLOCK_N>;
+    static bool configured = false;
+    if (!configured) {
+        NB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, HCfg<BLOCK_N>::SMEM_BYTES));
+        configured = true;
+    }
+    const int tiles = p.m_tiles * p.n_tiles;
+    kern<<<std::max(1, std::min(tiles, h->sm_count)), 320, HCfg<BLOCK_N>::SMEM_BYTES, h->stream>>>(p);
+    check_launch("conv3x3_halo_tcgen05_kernel");
+    count_launch(h);
+}
+
+inline bool aligned16(const void *p) { return ((uintptr_t)p & 15) == 0; }
+
+}  // namespace
+
+// Shapes this kernel takes: 3x3, stride 1, NHWC input with 32 <= C <= 128 and C % 4 == 0, TF32 mode,
+// output (or pooled output) addressable by TMA.
+bool conv_halo_supported(const nb_handle_s *h, const GemmArgs &a) {
+    if (!h->encode_tiled || h->cc_major != 10 || !a.a_is_conv || a.gather_table) return false;
+    const ConvGeom &g = a.g;
+    if (g.ksize != 3 || g.stride != 1 || g.pad > 1 || g.sc != 1) return false;
+    if (a.Kc < 32 || a.Kc > 128 || (a.Kc % 4) || (a.ldb % 4) || (a.N % 4)) return false;
+    if ((g.sw % 4) || (g.sh % 4) || (g.sn % 4) || !aligned16(a.a) || !aligned16(a.b)) return false;
+    if (g.OW < 14 || g.OH < 8) return false;
+    if (a.addend) return false;
+    if (a.y_pool ? ((g.OW | g.OH) & 1) || !aligned16(a.y_pool) : (!a.y || !aligned16(a.y) || (a.ldy % 4))) return false;
+    return true;
+}
+
+void conv_halo_tc(nb_handle_s *h, const GemmArgs &a) {
+    if (!conv_halo_supported(h, a)) throw Error(NB_ERR_UNSUPPORTED, "shape not supported by the 3x3 halo kernel");
+    const ConvGeom &g = a.g;
+    HaloParams p;
+    std::memset(&p, 0, sizeof p);
+    p.bw = 14; p.wt = 16;
+    p.halves = g.OH >= 16 ? 2 : 1;
+    p.rows_half = 8;
+    p.bh = 8 * p.halves;
+    p.tiles_w = (g.OW + p.bw - 1) / p.bw;
+    p.tiles_h = (g.OH + p.bh - 1) / p.bh;
+    p.NB = g.batch; p.OW = g.OW; p.OH = g.OH;
+    p.pad = g.pad;
+    p.c_blocks = (a.Kc + BLOCK_K - 1) / BLOCK_K;
+    p.m_tiles = p.tiles_w * p.tiles_h * g.batch;
+    const int block_n = a.N > 64 ? 128 : 64;
+    p.n_tiles = (a.N + block_n - 1) / block_n;
+    p.halo_bytes = BLOCK_K * 4 * p.wt * (p.bh + 2);
+    p.e.scale = a.scale; p.e.shift = a.shift; p.e.addend = nullptr; p.e.ld_addend = 0; p.e.addend_vec = 0;
+    p.e.act = a.act; p.e.round_out = a.round_out_tf32 ? 1 : 0;
+    p.e.y = a.y; p.e.ldy = a.ldy; p.e.tma_store = a.y_pool ? 0 : 1; p.e.pool = a.y_pool ? 1 : 0; p.e.N = a.N;
+    p.status = h->d_status;
+    {   // A halo: dims {C, W, H, N}, box {32, bw+2, bh+2, 1}
+        cuuint64_t dims[4] = {(cuuint64_t)a.Kc, (cuuint64_t)g.W, (cuuint64_t)g.H, (cuuint64_t)g.batch};
+        cuuint64_t strides[3] = {(cuuint64_t)g.sw * 4, (cuuint64_t)g.sh * 4, (cuuint64_t)g.sn * 4};
+        cuuint32_t bx[4] = {(cuuint32_t)BLOCK_K, (cuuint32_t)p.wt, (cuuint32_t)(p.bh + 2), 1};
+        encode(h, &p.tm_a, a.a, 4, dims, strides, bx);
+    }
+    {   // B: dims {C, N, 9}
+        cuuint64_t dims[3] = {(cuuint64_t)a.Kc, (cuuint64_t)a.N, 9};
+        cuuint64_t strides[2] = {(cuuint64_t)a.ldb * 4, (cuuint64_t)a.ldb * 4 * (cuuint64_t)a.N};
+        cuuint32_t bx[3] = {(cuuint32_t)BLOCK_K, (cuuint32_t)block_n, 1};
+        encode(h, &p.tm_b, a.b, 3, dims, strides, bx);
+    }
+    if (a.y_pool) {
+        cuuint64_t dims[4] = {(cuuint64_t)a.N, (cuuint64_t)(g.OW / 2), (cuuint64_t)(g.OH / 2), (cuuint64_t)g.batch};
+        cuuint64_t strides[3] = {(cuuint64_t)a.N * 4, (cuuint64_t)a.N * 4 * (cuuint64_t)(g.OW / 2),
+                                 (cuuint64_t)a.N * 4 * (cuuint64_t)(g.OW / 2) * (cuuint64_t)(g.OH / 2)};
+        cuuint32_t bx[4] = {32, (cuuint32_t)(p.bw / 2), (cuuint32_t)(p.rows_half / 2), 1};
+        encode(h, &p.tm_yp, a.y_pool, 4, dims, strides, bx);
+    } else {
+        cuuint64_t dims[4] = {(cuuint64_t)a.N, (cuuint64_t)g.OW, (cuuint64_t)g.OH, (cuuint64_t)g.batch};
+        cuuint64_t strides[3] = {(cuuint64_t)a.ldy * 4, (cuuint64_t)a.ldy * 4 * (cuuint64_t)g.OW,
+                                 (cuuint64_t)a.ldy * 4 * (cuuint64_t)g.OW * (cuuint64_t)g.OH};
+        cuuint32_t bx[4] = {32, (cuuint32_t)p.bw, (cuuint32_t)p.rows_half, 1};
+        encode(h, &p.tm_y, a.y, 4, dims, strides, bx);
+    }
+    ProfileScope prof(h, 2, a.algo_flops > 0 ? a.algo_flops : 2.0 * (double)a.M * a.N * a.Kc * 9);
+    if (block_n == 128) launch<128>(h, p);
+    else launch<64>(h, p);
+}
+
+}  // namespace nb

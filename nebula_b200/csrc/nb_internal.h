@@ -128,6 +128,9 @@ struct GemmArgs {
 // operands do not meet TMA's layout rules; callers then use gemm_simt.
 bool gemm_tc_supported(const nb_handle_s *h, const GemmArgs &a);
 void gemm_tc(nb_handle_s *h, const GemmArgs &a, bool three_pass);
+// 3x3 stride-1 convolutions with 32..128 input channels: one halo load per channel slice serves all nine taps.
+bool conv_halo_supported(const nb_handle_s *h, const GemmArgs &a);
+void conv_halo_tc(nb_handle_s *h, const GemmArgs &a);
 // CUDA-core fp32 path: any extents, strides and alignments.
 void gemm_simt(nb_handle_s *h, const GemmArgs &a);
 // Dispatch on the handle's math mode.
@@ -163,7 +166,8 @@ void launch_lstm_cell(nb_handle_s *h, const float *z, const float *c_prev, float
 void launch_sgemm(nb_handle_s *h, bool ta, bool tb, int M, int N, int K, float alpha, const float *A, int lda,
                   const float *B, int ldb, float beta, float *C, int ldc);
 
-// Brackets one contraction launch with events while profiling is on (kind 0 = tensor-core, 1 = CUDA-core).
+// Brackets one contraction launch with events while profiling is on
+// (kind 0 = generic tensor-core kernel, 1 = CUDA-core kernel, 2 = 3x3 halo tensor-core kernel).
 struct ProfileScope {
     nb_handle_s *h;
     nb_handle_s::Timed t;

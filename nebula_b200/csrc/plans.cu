@@ -221,7 +221,16 @@ void ConvPlan::forward(const float *x, float *y, const ForwardOpts &o) {
         w.ensure_split(h);
         a.b = w.hi.p;
         a.b_lo = w.lo.p;
-        gemm_tc(h, a, pth == PATH_TC3);
+        // few input channels: the generic kernel would re-load the activations once per tap from L2
+        bool halo = pth == PATH_TC && (d.channels <= 64 || (d.channels <= 128 && d.filters <= 128)) &&
+                    conv_halo_supported(h, a);
+        if (halo) {
+            const int bh = OH >= 16 ? 16 : 8;
+            const double eff = ((double)OW / ((OW + 13) / 14 * 14)) * ((double)OH / ((OH + bh - 1) / bh * bh));
+            halo = eff >= 0.6;
+        }
+        if (halo) conv_halo_tc(h, a);
+        else gemm_tc(h, a, pth == PATH_TC3);
     }
     if (!o.y_nhwc) launch_layout(h, yo, y, d.batch, d.filters, OH, OW, false, false);
 }

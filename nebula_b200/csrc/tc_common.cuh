@@ -1,0 +1,311 @@
+// Shared device code of the tcgen05 kernels: PTX wrappers (mbarrier, TMA, tcgen05),
+// descriptor builders, and the fused epilogue that both the generic GEMM kernel and
+// the 3x3 halo convolution kernel run on every 128-row x 32-column slab.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "device_math.cuh"
+#include "nb_internal.h"
+
+namespace nb {
+namespace tc {
+
+constexpr int BLOCK_M = 128;
+constexpr int BLOCK_K = 32;                  // fp32 elements = one 128-byte swizzle row
+constexpr int UMMA_K = 8;                    // tf32
+constexpr int A_STAGE_BYTES = BLOCK_M * BLOCK_K * 4;   // 16 KiB
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;  // ~2 s at 2 GHz
+
+
+// What the epilogue needs to know, common to both kernels.
+struct EpiParams {
+    const float *scale, *shift, *addend;    // scale/shift readable up to the next multiple of 32 columns
+    long ld_addend;
+    int addend_vec;             // addend rows are 16-byte aligned
+    int act, round_out;
+    float *y;
+    long ldy;
+    int tma_store;              // y meets TMA's rules: slabs leave through a tensor map; else plain stores
+    int pool;                   // fuse the following 2x2 stride-2 max-pool: only the pooled tensor is written
+    int N;                      // valid output columns
+};
+// Per thread: its row of the staging slab (-1: this accumulator row is not an output pixel), the
+// output pixel index for plain stores / addend reads, and whether that pixel exists.
+struct EpiRow { int srow; long grow; bool row_ok; };
+// The pixel box one slab covers and its origin in output coordinates.
+struct EpiBox { int bw, bh, bn, ow0, oh0, n0; };
+
+// ------------------------------------------------------------------ PTX glue
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false when the CTA is aborting (this wait or another ran out).
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status) {
+    if (mbar_try_wait(bar, parity)) return true;
+    long long t0 = clock64();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 32; i++)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+            *abort_flag = 1;
+            atomicExch(status, (int)DEV_TIMEOUT);
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
+}
+
+__device__ __forceinline__ void tma_load_4d(void *dst, const CUtensorMap *tm, uint64_t *bar, int c0, int c1, int c2,
+                                            int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(tm), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *tm, uint64_t *bar, int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(tm), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap *tm, const void *src, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                 ::"l"(tm), "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void tma_store_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// named barrier `id` over the 128 threads of one epilogue group
+__device__ __forceinline__ void epilogue_bar_sync(int id) { asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory"); }
+// AND-vote across the 128 threads of an epilogue group (named barrier `id`), so that leaving
+// the tile loop is a uniform decision and no thread is left alone at a later bar.sync.
+__device__ __forceinline__ bool epilogue_all(bool pred, int id) {
+    uint32_t r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.b32 p, %1, 0;\n\t"
+        "bar.red.and.pred q, %2, 128, p;\n\t"
+        "selp.b32 %0, 1, 0, q;\n\t}"
+        : "=r"(r)
+        : "r"((uint32_t)pred), "r"(id)
+        : "memory");
+    return r != 0;
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows 128 B
+// apart, 8-row groups 1024 B apart (bits: start>>4 [0,14), LBO>>4 [16,30),
+// SBO>>4 [32,46), version=1 [46,48), layout=SWIZZLE_128B(2) [61,64)).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// Instruction descriptor for kind::tf32: D=f32 (bits 4-5 = 1), A=B=tf32 (bits
+// 7-9, 10-12 = 2), both K-major (bits 15,16 = 0), N>>3 at bit 17, M>>4 at bit 24.
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
+    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+
+// One 128-row x 32-column slab of accumulators (already in registers): folded batch-norm
+// scale/shift + bias, optional addend, activation, optional TF32 rounding, then either a swizzled
+// staging slab that leaves by TMA (optionally 2x2/2 max-pooled first) or plain global stores.
+// Called by the 128 threads of one epilogue group; `t` is the thread's index in the group.
+__device__ __forceinline__ void epilogue_chunk(const EpiParams &e, const CUtensorMap *tm_y, const CUtensorMap *tm_yp,
+                                               uint32_t (&v)[32], int col0, const EpiRow &rw, const EpiBox &bx,
+                                               float4 *slab, int bar_id, bool store_thread, int t) {
+    const bool full_cols = col0 + 32 <= e.N;
+    // affine part: folded batch-norm scale/shift + bias (vectors padded to a multiple of 32)
+    if (e.scale) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+            const float4 sc = __ldg(reinterpret_cast<const float4 *>(e.scale + col0 + j));
+            const float4 sh = __ldg(reinterpret_cast<const float4 *>(e.shift + col0 + j));
+            v[j] = __float_as_uint(fmaf(__uint_as_float(v[j]), sc.x, sh.x));
+            v[j + 1] = __float_as_uint(fmaf(__uint_as_float(v[j + 1]), sc.y, sh.y));
+            v[j + 2] = __float_as_uint(fmaf(__uint_as_float(v[j + 2]), sc.z, sh.z));
+            v[j + 3] = __float_as_uint(fmaf(__uint_as_float(v[j + 3]), sc.w, sh.w));
+        }
+    } else if (e.shift) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+            const float4 sh = __ldg(reinterpret_cast<const float4 *>(e.shift + col0 + j));
+            v[j] = __float_as_uint(__uint_as_float(v[j]) + sh.x);
+            v[j + 1] = __float_as_uint(__uint_as_float(v[j + 1]) + sh.y);
+            v[j + 2] = __float_as_uint(__uint_as_float(v[j + 2]) + sh.z);
+            v[j + 3] = __float_as_uint(__uint_as_float(v[j + 3]) + sh.w);
+        }
+    }
+    if (e.addend && rw.row_ok) {
+        const float *arow = e.addend + rw.grow * e.ld_addend + col0;
+        if (full_cols && e.addend_vec) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+                const float4 ad = *reinterpret_cast<const float4 *>(arow + j);
+                v[j] = __float_as_uint(__uint_as_float(v[j]) + ad.x);
+                v[j + 1] = __float_as_uint(__uint_as_float(v[j + 1]) + ad.y);
+                v[j + 2] = __float_as_uint(__uint_as_float(v[j + 2]) + ad.z);
+                v[j + 3] = __float_as_uint(__uint_as_float(v[j + 3]) + ad.w);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; j++)
+                if (col0 + j < e.N) v[j] = __float_as_uint(__uint_as_float(v[j]) + arow[j]);
+        }
+    }
+    // activation: the common ones inline, the rest through one out-of-line call per value
+    if (e.act == NB_ACT_RELU) {
+#pragma unroll
+        for (int j = 0; j < 32; j++) v[j] = __uint_as_float(v[j]) > 0.0f ? v[j] : 0u;
+    } else if (e.act == NB_ACT_LEAKY) {
+#pragma unroll
+        for (int j = 0; j < 32; j++) {
+            const float x = __uint_as_float(v[j]);
+            v[j] = __float_as_uint(x > 0.0f ? x : (float)(0.1 * (double)x));
+        }
+    } else if (e.act != NB_ACT_LINEAR) {
+#pragma unroll
+        for (int j = 0; j < 32; j++) v[j] = __float_as_uint(apply_activation_call(__uint_as_float(v[j]), e.act));
+    }
+    if (e.round_out) {
+#pragma unroll
+        for (int j = 0; j < 32; j++) v[j] = __float_as_uint(round_tf32(__uint_as_float(v[j])));
+    }
+    if (e.pool || e.tma_store) {
+        // the group's previous store must have finished reading the staging buffer
+        if (store_thread) tma_store_wait_read<0>();
+        epilogue_bar_sync(bar_id);
+        if (rw.srow >= 0) {
+#pragma unroll
+        for (int j = 0; j < 8; j++)     // 16-byte chunk j of row r lives at chunk j ^ (r % 8)
+            slab[rw.srow * 8 + (j ^ (rw.srow & 7))] = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                                     __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+        }
+        if (!e.pool) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            epilogue_bar_sync(bar_id);
+            if (store_thread) {
+                tma_store_4d(tm_y, slab, col0, bx.ow0, bx.oh0, bx.n0);
+                tma_store_commit();
+            }
+        } else {
+            // conv + 2x2/2 max-pool (pooling_layer.cc:117-146): each thread reduces two 16-byte
+            // chunks of one pooled pixel from the full-resolution slab, then the pooled rows
+            // overwrite the head of the same buffer and leave by TMA.
+            epilogue_bar_sync(bar_id);
+            const int pr = t >> 2, hw = bx.bw >> 1, hh = bx.bh >> 1;
+            const int pw = pr % hw, ph = (pr / hw) % hh, pn = pr / (hw * hh);
+            float4 m[2];
+            if (pn < bx.bn) {
+                const int r00 = (pn * bx.bh + 2 * ph) * bx.bw + 2 * pw;
+#pragma unroll
+                for (int e = 0; e < 2; e++) {
+                    const int c = (t & 3) * 2 + e;
+                    m[e] = make_float4(-1e8f, -1e8f, -1e8f, -1e8f);     // the reference's identity
+#pragma unroll
+                    for (int w4 = 0; w4 < 4; w4++) {
+                        const int rr = r00 + (w4 >> 1) * bx.bw + (w4 & 1);
+                        const float4 x4 = slab[rr * 8 + (c ^ (rr & 7))];
+                        m[e].x = x4.x > m[e].x ? x4.x : m[e].x; m[e].y = x4.y > m[e].y ? x4.y : m[e].y;
+                        m[e].z = x4.z > m[e].z ? x4.z : m[e].z; m[e].w = x4.w > m[e].w ? x4.w : m[e].w;
+                    }
+                }
+            }
+            epilogue_bar_sync(bar_id);      // every source row has been read
+            if (pn < bx.bn) {
+#pragma unroll
+                for (int e = 0; e < 2; e++) {
+                    const int c = (t & 3) * 2 + e;
+                    slab[pr * 8 + (c ^ (pr & 7))] = m[e];
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            epilogue_bar_sync(bar_id);
+            if (store_thread) {
+                tma_store_4d(tm_yp, slab, col0, bx.ow0 >> 1, bx.oh0 >> 1, bx.n0);
+                tma_store_commit();
+            }
+        }
+    } else if (rw.row_ok) {
+        float *yrow = e.y + rw.grow * e.ldy + col0;
+#pragma unroll
+        for (int j = 0; j < 32; j++)
+            if (full_cols || col0 + j < e.N) yrow[j] = __uint_as_float(v[j]);
+    }
+}
+
+}  // namespace tc
+}  // namespace nb

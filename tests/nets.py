@@ -17,6 +17,11 @@ def tiny_vgg(batch=4):
     return vgg16(batch=batch, height=32, width=32, fc=128, classes=10, widths=(32, 32, 64, 64, 64))
 
 
+def mid_vgg(batch=2):
+    """Big enough (56x56, 64/128 channels) for the 3x3 halo kernel and its fused pooling."""
+    return vgg16(batch=batch, height=56, width=56, fc=64, classes=10, widths=(64, 128, 64, 64, 64))
+
+
 def tiny_resnet(batch=2):
     return resnet50(batch=batch, height=64, width=64, base=32, blocks=(2, 2, 2, 2), classes=10)
 
@@ -29,4 +34,4 @@ def small_alexnet(batch=2):
     return alexnet(batch=batch)
 
 
-NETS = {"toy": toy_convnet, "tiny_vgg": tiny_vgg, "tiny_resnet": tiny_resnet, "tiny_lstm": tiny_lstm}
+NETS = {"toy": toy_convnet, "tiny_vgg": tiny_vgg, "mid_vgg": mid_vgg, "tiny_resnet": tiny_resnet, "tiny_lstm": tiny_lstm}

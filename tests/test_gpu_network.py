@@ -76,7 +76,7 @@ def test_alexnet_full_size_two_images(handle):
 
 
 @pytest.mark.parametrize("mode", ["tf32", "tf32x3"])
-@pytest.mark.parametrize("name", ["tiny_vgg", "toy"])
+@pytest.mark.parametrize("name", ["tiny_vgg", "toy", "mid_vgg"])
 def test_fused_pooling_is_bit_identical(handle, name, mode):
     """conv + 2x2/2 max-pool in one kernel gives exactly what the two kernels give."""
     from nebula_b200 import api

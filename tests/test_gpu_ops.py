@@ -34,6 +34,9 @@ CONV_CASES = [
     (2, 32, 31, 31, 16, 11, 4, 0, False, "relu"),       # 11x11 stride 4
     (5, 128, 7, 7, 256, 3, 1, 1, False, "relu"),        # several images per pixel box
     (1, 32, 40, 36, 300, 3, 1, 0, False, "tanh"),       # no padding, F tail over 256
+    (2, 64, 28, 42, 64, 3, 1, 1, False, "relu"),        # 3x3 halo kernel: two 128-row halves, exact tiles in W
+    (1, 128, 33, 56, 160, 3, 1, 1, True, "leaky"),      # halo kernel: C=128, ragged tiles in H, filter tail
+    (3, 32, 16, 28, 40, 3, 1, 0, False, "linear"),      # halo kernel without padding
 ]
 
 
