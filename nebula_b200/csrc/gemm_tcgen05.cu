@@ -59,6 +59,10 @@ struct TcParams {
     int num_k_blocks;           // ksize*ksize*c_blocks
     int m_tiles, n_tiles;
     int tx_bytes_a;             // bytes one A box load delivers
+    // The tensor core's fp32 accumulator rounds toward zero at every K=8 step (a bias that grows with K).
+    // After every kb_per_part K blocks the partial sums are promoted to registers (round-to-nearest adds)
+    // and the TMEM accumulator restarts; parts = number of such partial sums per tile (1: no promotion).
+    int kb_per_part, parts;
     EpiParams e;                // fused epilogue
     // gather mode: warps 6-9 build the A tile in shared memory from a strided activation tensor
     // (channel counts TMA cannot address, e.g. the 3-channel input layer); rows are output pixels
@@ -76,13 +80,13 @@ struct Cfg {
     static constexpr int STAGE_BYTES = (A_STAGE_BYTES + B_STAGE_BYTES) * (THREE ? 2 : 1);
     static constexpr int STAGES = (196 * 1024) / STAGE_BYTES < 8 ? (196 * 1024) / STAGE_BYTES : 8;
     static constexpr int TMEM_COLS = 2 * BLOCK_N;
-    static constexpr int MAX_THREADS = 448;
+    static constexpr int MAX_THREADS = (BLOCK_N == 256 && !THREE) ? 320 : 448;   // 256-wide tiles never run the extra operand warps
     static constexpr int OUT_STAGE_BYTES = BLOCK_M * 32 * 4;     // one 128 x 32 output slab
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 2 * OUT_STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
 };
 
 // ------------------------------------------------------------------- kernel
-template <int BLOCK_N, bool THREE>
+template <int BLOCK_N, bool THREE, bool PROMOTE>
 __global__ void __launch_bounds__(Cfg<BLOCK_N, THREE>::MAX_THREADS, 1)
 gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
     using C = Cfg<BLOCK_N, THREE>;
@@ -171,8 +175,18 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
                 if (!(ok = mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag, p.status))) break;
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BLOCK_N);
-                for (int kb = 0; kb < p.num_k_blocks; kb++) {
+                uint32_t d_tmem = tmem_base + (uint32_t)(acc * BLOCK_N);
+                int kb_in_part = 0;
+                for (int kb = 0; kb < p.num_k_blocks; kb++, kb_in_part++) {
+                    if (kb_in_part == p.kb_per_part) {
+                        // hand this partial sum to the epilogue warps and restart in the other accumulator
+                        umma_commit(&acc_full[acc]);
+                        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+                        if (!(ok = mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag, p.status))) break;
+                        tc_fence_after();
+                        d_tmem = tmem_base + (uint32_t)(acc * BLOCK_N);
+                        kb_in_part = 0;
+                    }
                     uint64_t *ready = (THREE && !p.gather) ? &split[stage] : &full[stage];
                     if (!(ok = mbar_wait(ready, phase, abort_flag, p.status))) break;
                     tc_fence_after();
@@ -186,11 +200,11 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
                         if (THREE) {
                             const uint64_t da_lo = make_smem_desc(sb + C::B_STAGE_BYTES + koff);
                             const uint64_t db_lo = make_smem_desc(sb + C::B_STAGE_BYTES + A_STAGE_BYTES + koff);
-                            umma_tf32(d_tmem, da_lo, db, idesc, (kb | k) != 0);
+                            umma_tf32(d_tmem, da_lo, db, idesc, (kb_in_part | k) != 0);
                             umma_tf32(d_tmem, da, db_lo, idesc, 1);
                             umma_tf32(d_tmem, da, db, idesc, 1);
                         } else {
-                            umma_tf32(d_tmem, da, db, idesc, (kb | k) != 0);
+                            umma_tf32(d_tmem, da, db, idesc, (kb_in_part | k) != 0);
                         }
                     }
                     umma_commit(&empty[stage]);     // frees the stage once these MMAs have read it
@@ -214,6 +228,7 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
         const int t = (ew & 3) * 32 + lane;     // index inside the group
         const int rw = r % p.bw, rh = (r / p.bw) % p.bh, rn = r / (p.bw * p.bh);
         const bool store_thread = t == 0;
+        constexpr int CH = BLOCK_N >= 64 ? BLOCK_N / 64 : 1;    // 32-column slabs per group
         float4 *slab = reinterpret_cast<float4 *>(out_stage + grp * C::OUT_STAGE_BYTES);
         int acc = 0;
         uint32_t acc_phase = 0;
@@ -226,22 +241,59 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
             const int ow = tw * p.bw + rw, oh = th * p.bh + rh, n = tn * p.bn + rn;
             const bool row_ok = (rn < p.bn) && ow < p.OW && oh < p.OH && n < p.NB;
             const long row = ((long)n * p.OH + oh) * p.OW + ow;
-            if (!(ok = epilogue_all(mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status), bar_id))) break;
-            tc_fence_after();
+            const EpiRow erow{r, row, row_ok};
+            const EpiBox ebox{p.bw, p.bh, p.bn, tw * p.bw, th * p.bh, tn * p.bn};
+            if (!PROMOTE || p.parts == 1) {
+                if (!(ok = epilogue_all(mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status), bar_id))) break;
+                tc_fence_after();
 #pragma unroll 1
-            for (int chunk = grp; chunk < BLOCK_N / 32; chunk += 2) {
-                const int col0 = n_tile * BLOCK_N + chunk * 32;
-                if (col0 >= p.e.N) break;         // uniform across the group
-                uint32_t v[32];
-                tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BLOCK_N + chunk * 32), v);
-                tmem_ld_wait();
-                const EpiRow rw{r, row, row_ok};
-                const EpiBox bx{p.bw, p.bh, p.bn, tw * p.bw, th * p.bh, tn * p.bn};
-                epilogue_chunk(p.e, &p.tm_y, &p.tm_yp, v, col0, rw, bx, slab, bar_id, store_thread, t);
+                for (int chunk = grp; chunk < BLOCK_N / 32; chunk += 2) {
+                    const int col0 = n_tile * BLOCK_N + chunk * 32;
+                    if (col0 >= p.e.N) break;         // uniform across the group
+                    uint32_t v[32];
+                    tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BLOCK_N + chunk * 32), v);
+                    tmem_ld_wait();
+                    epilogue_chunk(p.e, &p.tm_y, &p.tm_yp, v, col0, erow, ebox, slab, bar_id, store_thread, t);
+                }
+                tc_fence_before();
+                mbar_arrive(&acc_empty[acc]);
+                if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+            } else if constexpr (PROMOTE) {
+                // promoted accumulation: this group's slabs of every partial sum are added in registers
+                uint32_t sum[CH][32];
+                for (int part = 0; part < p.parts && ok; part++) {
+                    if (!(ok = epilogue_all(mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status), bar_id))) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int ci = 0; ci < CH; ci++) {
+                        const int chunk = grp + 2 * ci;
+                        if (chunk * 32 < BLOCK_N && n_tile * BLOCK_N + chunk * 32 < p.e.N) {
+                            uint32_t v[32];
+                            tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BLOCK_N + chunk * 32), v);
+                            tmem_ld_wait();
+                            if (part == 0) {
+#pragma unroll
+                                for (int j = 0; j < 32; j++) sum[ci][j] = v[j];
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 32; j++)
+                                    sum[ci][j] = __float_as_uint(__uint_as_float(sum[ci][j]) + __uint_as_float(v[j]));
+                            }
+                        }
+                    }
+                    tc_fence_before();
+                    mbar_arrive(&acc_empty[acc]);
+                    if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+                }
+                if (!ok) break;
+#pragma unroll
+                for (int ci = 0; ci < CH; ci++) {
+                    const int chunk = grp + 2 * ci;
+                    const int col0 = n_tile * BLOCK_N + chunk * 32;
+                    if (chunk * 32 < BLOCK_N && col0 < p.e.N)
+                        epilogue_chunk(p.e, &p.tm_y, &p.tm_yp, sum[ci], col0, erow, ebox, slab, bar_id, store_thread, t);
+                }
             }
-            tc_fence_before();
-            mbar_arrive(&acc_empty[acc]);
-            if (++acc == 2) { acc = 0; acc_phase ^= 1; }
         }
         if (store_thread) tma_store_wait_all();     // staged tiles must have left shared memory
     } else if (p.gather) {
@@ -375,10 +427,10 @@ void encode(nb_handle_s *h, CUtensorMap *tm, const void *base, int rank, const c
     if (r != CUDA_SUCCESS) throw Error(NB_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
 }
 
-template <int BLOCK_N, bool THREE>
+template <int BLOCK_N, bool THREE, bool PROMOTE>
 void launch(nb_handle_s *h, const TcParams &p) {
     using C = Cfg<BLOCK_N, THREE>;
-    auto kern = gemm_tf32_tcgen05_kernel<BLOCK_N, THREE>;
+    auto kern = gemm_tf32_tcgen05_kernel<BLOCK_N, THREE, PROMOTE>;
     static bool configured = false;
     if (!configured) {
         NB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
@@ -458,8 +510,11 @@ void gemm_tc(nb_handle_s *h, const GemmArgs &a, bool three_pass) {
     p.status = h->d_status;
 
     // tile width in filters: widest tile that still gives every SM work
+    // Promoted accumulation: always for 3xTF32 (its point is fp32-level agreement); in TF32 mode only for
+    // very long contractions, where the accumulator's round-toward-zero bias (~K * 7.5e-9) nears TF32's own error.
+    const bool promote = three_pass || (long)p.num_k_blocks * BLOCK_K >= 8192;
     int block_n = 256;
-    if (three_pass) block_n = 128;
+    if (three_pass || gather || promote) block_n = 128;
     while (block_n > 64) {
         const long tiles = (long)p.m_tiles * ((a.N + block_n - 1) / block_n);
         if (a.N > block_n / 2 && tiles >= h->sm_count) break;
@@ -467,6 +522,9 @@ void gemm_tc(nb_handle_s *h, const GemmArgs &a, bool three_pass) {
         block_n /= 2;
     }
     p.n_tiles = (a.N + block_n - 1) / block_n;
+    // accumulation chains of at most 512 (TF32) / 128 (3xTF32) K elements in the tensor core
+    p.kb_per_part = !promote ? p.num_k_blocks : (three_pass ? 4 : 16);
+    p.parts = (p.num_k_blocks + p.kb_per_part - 1) / p.kb_per_part;
 
     p.gather = gather ? 1 : 0;
     if (gather) {
@@ -512,12 +570,15 @@ void gemm_tc(nb_handle_s *h, const GemmArgs &a, bool three_pass) {
 
     ProfileScope prof(h, 0, a.algo_flops > 0 ? a.algo_flops : 2.0 * (double)a.M * a.N * a.Kc * taps);
     if (three_pass) {
-        if (block_n == 128) launch<128, true>(h, p);
-        else launch<64, true>(h, p);
+        if (block_n == 128) launch<128, true, true>(h, p);
+        else launch<64, true, true>(h, p);
+    } else if (promote) {
+        if (block_n == 128) launch<128, false, true>(h, p);
+        else launch<64, false, true>(h, p);
     } else {
-        if (block_n == 256) launch<256, false>(h, p);
-        else if (block_n == 128) launch<128, false>(h, p);
-        else launch<64, false>(h, p);
+        if (block_n == 256) launch<256, false, false>(h, p);
+        else if (block_n == 128) launch<128, false, false>(h, p);
+        else launch<64, false, false>(h, p);
     }
 }
 
