@@ -250,7 +250,7 @@ inline bool aligned16(const void *p) { return ((uintptr_t)p & 15) == 0; }
 // Shapes this kernel takes: 3x3, stride 1, NHWC input with 32 <= C <= 128 and C % 4 == 0, TF32 mode,
 // output (or pooled output) addressable by TMA.
 bool conv_halo_supported(const nb_handle_s *h, const GemmArgs &a) {
-    if (!h->encode_tiled || h->cc_major != 10 || !a.a_is_conv || a.gather_table) return false;
+    if (!h->encode_tiled || h->cc_major != 10 || !a.a_is_conv || a.a_gather) return false;
     const ConvGeom &g = a.g;
     if (g.ksize != 3 || g.stride != 1 || g.pad > 1 || g.sc != 1) return false;
     if (a.Kc < 32 || a.Kc > 128 || (a.Kc % 4) || (a.ldb % 4) || (a.N % 4)) return false;

@@ -282,6 +282,23 @@ __global__ void fc_permute_kernel(const float *w, float *dst, int out, int C, in
     }
 }
 
+// -------------------------------------------------------------- split-K tail
+// y[m][n] = act(scale[n] * sum_s ws[s][m][n] + shift[n]): the epilogue of a split-K contraction
+// (slices are added in a fixed order, so the result does not depend on scheduling).
+__global__ void splitk_reduce_kernel(const float *ws, int S, size_t MN, int N, const float *scale, const float *shift,
+                                     int act, int round, float *y) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < MN; i += stride) {
+        float acc = ws[i];
+        for (int s = 1; s < S; s++) acc += ws[(size_t)s * MN + i];
+        const int n = (int)(i % N);
+        if (scale) acc = fmaf(acc, scale[n], shift[n]);
+        else if (shift) acc += shift[n];
+        acc = apply_activation_fast(acc, act);
+        y[i] = round ? round_tf32(acc) : acc;
+    }
+}
+
 // ---------------------------------------------------------------- LSTM cell
 // lstm_layer_t::forward (lstm_layer.cc:286-311): i,f,o = logistic(z), g = tanh(z),
 // c_t = c_{t-1}*f + i*g, h_t = tanh(c_t)*o.  Products and the sum are separate
@@ -459,6 +476,13 @@ void launch_fc_permute(nb_handle_s *h, const float *w, float *dst, int out, int 
     const size_t total = (size_t)out * C * H * W;
     fc_permute_kernel<<<grid_for(total, h), TPB, 0, h->stream>>>(w, dst, out, C, H * W, total);
     check_launch("fc_permute_kernel");
+    count_launch(h);
+}
+void launch_splitk_reduce(nb_handle_s *h, const float *ws, int S, int M, int N, const float *scale, const float *shift,
+                          int act, bool round, float *y) {
+    const size_t MN = (size_t)M * N;
+    splitk_reduce_kernel<<<grid_for(MN, h), TPB, 0, h->stream>>>(ws, S, MN, N, scale, shift, act, round ? 1 : 0, y);
+    check_launch("splitk_reduce_kernel");
     count_launch(h);
 }
 void launch_lstm_cell(nb_handle_s *h, const float *z, const float *c_prev, float *c_out, float *h_out, float *h_round,

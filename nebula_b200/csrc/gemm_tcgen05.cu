@@ -44,6 +44,8 @@ using namespace tc;
 
 namespace {
 
+constexpr int GATHER_MAX_K = 384;      // largest k*k*C (rounded up to 32) the gather table in the kernel parameters holds
+
 struct TcParams {
     CUtensorMap tm_a;
     CUtensorMap tm_b;
@@ -59,6 +61,7 @@ struct TcParams {
     int num_k_blocks;           // ksize*ksize*c_blocks
     int m_tiles, n_tiles;
     int tx_bytes_a;             // bytes one A box load delivers
+    int b_from_th;              // split-K: the weight tile's third coordinate is the tile's row index th
     // The tensor core's fp32 accumulator rounds toward zero at every K=8 step (a bias that grows with K).
     // After every kb_per_part K blocks the partial sums are promoted to registers (round-to-nearest adds)
     // and the TMEM accumulator restarts; parts = number of such partial sums per tile (1: no promotion).
@@ -68,9 +71,11 @@ struct TcParams {
     // (channel counts TMA cannot address, e.g. the 3-channel input layer); rows are output pixels
     int gather;
     const float *gx;
-    const int2 *gtab;           // per column kk: {element offset of (c, kh-pad, kw-pad), (kh-pad) | (kw-pad) << 16}
-    long gsn, gsh, gsw;
+    long gsn, gsh, gsw;         // element strides of the gathered tensor
+    int gks, gpad, gK;          // filter size, padding, k*k*C: column kk = (kh, kw, c), c fastest
     int gH, gW, gOH, gOW, gstride, gM, ground;
+    // per column: {element offset of (c, kh-pad, kw-pad) from the pixel's origin, (kh-pad) & 0xffff | (kw-pad) << 16}
+    int2 gtab[GATHER_MAX_K];
     int *status;
 };
 
@@ -154,7 +159,7 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
                     uint8_t *sb = sa + A_STAGE_BYTES;
                     mbar_expect_tx(&full[stage], (uint32_t)((p.gather ? 0 : p.tx_bytes_a) + C::B_STAGE_BYTES * (THREE ? 2 : 1)));
                     if (!p.gather) tma_load_4d(sa, &p.tm_a, &full[stage], cb * BLOCK_K, w0 + kw, h0 + kh, n0);
-                    tma_load_3d(sb, &p.tm_b, &full[stage], cb * BLOCK_K, n_tile * BLOCK_N, tap);
+                    tma_load_3d(sb, &p.tm_b, &full[stage], cb * BLOCK_K, n_tile * BLOCK_N, p.b_from_th ? th : tap);
                     if (THREE)
                         tma_load_3d(sb + C::B_STAGE_BYTES + A_STAGE_BYTES, &p.tm_b_lo, &full[stage], cb * BLOCK_K,
                                     n_tile * BLOCK_N, tap);
@@ -318,24 +323,37 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
                 ih0 = oh * p.gstride; iw0 = ow * p.gstride;
                 base = p.gx + (long)n * p.gsn + (long)ih0 * p.gsh + (long)iw0 * p.gsw;
             }
+            // does every tap of this pixel fall inside the image?  (true for all but border pixels)
+            const int ihf = ih0 - p.gpad, iwf = iw0 - p.gpad;
+            const bool interior = valid && ihf >= 0 && iwf >= 0 && ihf + p.gks <= p.gH && iwf + p.gks <= p.gW;
             for (int kb = 0; kb < p.num_k_blocks; kb++) {
                 if (!(ok = mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status))) break;
                 float4 *a_row = reinterpret_cast<float4 *>(smem + stage * C::STAGE_BYTES + t * 128);
                 float4 *a_lo_row = reinterpret_cast<float4 *>(smem + stage * C::STAGE_BYTES + A_STAGE_BYTES + C::B_STAGE_BYTES + t * 128);
+                const int2 *tab = p.gtab + kb * BLOCK_K;        // kernel-parameter (constant bank) table
+                float x[32];
+                if (interior) {
+#pragma unroll
+                    for (int i = 0; i < 32; i++)                // 32 independent loads in flight
+                        x[i] = (kb * BLOCK_K + i < p.gK) ? __ldg(base + tab[i].x) : 0.0f;
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; i++) {
+                        const int ih = ih0 + (int)(short)(tab[i].y & 0xffff), iw = iw0 + (tab[i].y >> 16);
+                        const bool inb = valid && kb * BLOCK_K + i < p.gK && ih >= 0 && ih < p.gH && iw >= 0 && iw < p.gW;
+                        x[i] = inb ? __ldg(base + tab[i].x) : 0.0f;
+                    }
+                }
 #pragma unroll
                 for (int j = 0; j < 8; j++) {
                     float v[4], lo[4];
 #pragma unroll
                     for (int e = 0; e < 4; e++) {
-                        const int2 tb = __ldg(p.gtab + kb * BLOCK_K + j * 4 + e);
-                        const int ih = ih0 + (int)(short)(tb.y & 0xffff), iw = iw0 + (tb.y >> 16);
-                        float x = 0.0f;
-                        if (valid && ih >= 0 && ih < p.gH && iw >= 0 && iw < p.gW) x = __ldg(base + tb.x);
                         if (THREE) {
-                            v[e] = __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
-                            lo[e] = x - v[e];
+                            v[e] = __uint_as_float(__float_as_uint(x[4 * j + e]) & 0xFFFFE000u);
+                            lo[e] = x[4 * j + e] - v[e];
                         } else {
-                            v[e] = p.ground ? round_tf32(x) : x;
+                            v[e] = p.ground ? round_tf32(x[4 * j + e]) : x[4 * j + e];
                         }
                     }
                     a_row[j ^ (t & 7)] = make_float4(v[0], v[1], v[2], v[3]);
@@ -450,7 +468,7 @@ inline bool aligned16(const void *p) { return ((uintptr_t)p & 15) == 0; }
 
 bool gemm_tc_supported(const nb_handle_s *h, const GemmArgs &a) {
     if (!h->encode_tiled || h->cc_major != 10) return false;
-    if (a.gather_table) return (a.Kc % 32) == 0 && (a.ldb % 4) == 0 && aligned16(a.b);
+    if (a.a_gather) return (a.Kc % 32) == 0 && a.Kc <= GATHER_MAX_K && (a.ldb % 4) == 0 && aligned16(a.b);
     if (a.Kc < 32 || (a.Kc % 4) != 0 || (a.ldb % 4) != 0 || !aligned16(a.b) || !aligned16(a.a)) return false;
     if (a.a_is_conv) {
         const ConvGeom &g = a.g;
@@ -465,13 +483,13 @@ bool gemm_tc_supported(const nb_handle_s *h, const GemmArgs &a) {
 
 void gemm_tc(nb_handle_s *h, const GemmArgs &a, bool three_pass) {
     if (!gemm_tc_supported(h, a)) throw Error(NB_ERR_UNSUPPORTED, "operands do not satisfy the TMA layout rules");
-    if (a.y_pool && a.gather_table) throw Error(NB_ERR_UNSUPPORTED, "fused pooling is not available with the gathered A operand");
+    if (a.y_pool && a.a_gather) throw Error(NB_ERR_UNSUPPORTED, "fused pooling is not available with the gathered A operand");
     if (three_pass && !a.b_lo) throw Error(NB_ERR_INVALID_ARG, "three-pass GEMM needs the low-order weight split");
     TcParams p;
     std::memset(&p, 0, sizeof p);
 
     ConvGeom g;
-    const bool gather = a.gather_table != nullptr;
+    const bool gather = a.a_gather;
     if (a.a_is_conv && !gather) {
         g = a.g;
     } else {
@@ -480,16 +498,28 @@ void gemm_tc(nb_handle_s *h, const GemmArgs &a, bool three_pass) {
         g.ksize = 1; g.stride = 1; g.pad = 0;
         g.sc = 1; g.sw = a.lda; g.sh = (long)a.lda * a.M; g.sn = (long)a.lda * a.M;
     }
+    // Split-K (plain matrices only): split s contracts columns [s*kc, (s+1)*kc) and writes its own
+    // [M,N] slab of y.  Expressed through the same machinery as an "image" of height S whose row
+    // stride is kc elements; the weight tile's third coordinate is the split index.
+    const int S = (!a.a_is_conv && !gather && a.split_k > 1) ? a.split_k : 1;
+    const int kc = a.Kc / S;
+    if (S > 1) {
+        if (a.Kc % (S * BLOCK_K) || a.y_pool || a.addend || three_pass)
+            throw Error(NB_ERR_INVALID_ARG, "split-K needs K divisible by 32*splits and a plain epilogue");
+        g.C = kc; g.H = S; g.OH = S; g.sh = kc;
+    }
     const int taps = g.ksize * g.ksize;
     const bool pool = a.y_pool != nullptr;
     Box box = choose_box(g.OW, g.OH, g.batch, g.stride, pool);
+    if (S > 1) box = Box{std::min(128, g.OW), 1, 1};
     p.bw = box.bw; p.bh = box.bh; p.bn = box.bn;
     p.tiles_w = (g.OW + box.bw - 1) / box.bw;
     p.tiles_h = (g.OH + box.bh - 1) / box.bh;
     p.tiles_n = (g.batch + box.bn - 1) / box.bn;
     p.OW = g.OW; p.OH = g.OH; p.NB = g.batch;
     p.ksize = g.ksize; p.stride = g.stride; p.pad = g.pad;
-    p.c_blocks = (a.Kc + BLOCK_K - 1) / BLOCK_K;
+    p.c_blocks = (kc + BLOCK_K - 1) / BLOCK_K;
+    p.b_from_th = S > 1 ? 1 : 0;
     p.num_k_blocks = taps * p.c_blocks;
     p.m_tiles = p.tiles_w * p.tiles_h * p.tiles_n;
     p.e.N = a.N;
@@ -512,7 +542,7 @@ void gemm_tc(nb_handle_s *h, const GemmArgs &a, bool three_pass) {
     // tile width in filters: widest tile that still gives every SM work
     // Promoted accumulation: always for 3xTF32 (its point is fp32-level agreement); in TF32 mode only for
     // very long contractions, where the accumulator's round-toward-zero bias (~K * 7.5e-9) nears TF32's own error.
-    const bool promote = three_pass || (long)p.num_k_blocks * BLOCK_K >= 8192;
+    const bool promote = three_pass || (long)p.num_k_blocks * BLOCK_K >= 8192;   // per split when K is split
     int block_n = 256;
     if (three_pass || gather || promote) block_n = 128;
     while (block_n > 64) {
@@ -528,13 +558,23 @@ void gemm_tc(nb_handle_s *h, const GemmArgs &a, bool three_pass) {
 
     p.gather = gather ? 1 : 0;
     if (gather) {
-        p.gx = a.a; p.gtab = (const int2 *)a.gather_table;
+        p.gx = a.a;
         p.gsn = a.g.sn; p.gsh = a.g.sh; p.gsw = a.g.sw;
+        p.gks = a.g.ksize; p.gpad = a.g.pad; p.gK = a.g.C * a.g.ksize * a.g.ksize;
+        for (int kk = 0; kk < a.Kc; kk++) {
+            int off = 0, dh = 30000, dw = 0;        // padding columns: a row offset that is never inside an image
+            if (kk < p.gK) {
+                const int tap = kk / a.g.C, c = kk - tap * a.g.C;
+                dh = tap / a.g.ksize - a.g.pad; dw = tap % a.g.ksize - a.g.pad;
+                off = (int)(c * a.g.sc + dh * a.g.sh + dw * a.g.sw);
+            }
+            p.gtab[kk] = make_int2(off, (dh & 0xffff) | (dw << 16));
+        }
         p.gH = a.g.H; p.gW = a.g.W; p.gOH = a.g.OH; p.gOW = a.g.OW; p.gstride = a.g.stride; p.gM = a.M;
         p.ground = three_pass ? 0 : 1;
     }
     if (!gather) {   // A: dims {C, W, H, N}
-        cuuint64_t dims[4] = {(cuuint64_t)a.Kc, (cuuint64_t)g.W, (cuuint64_t)g.H, (cuuint64_t)g.batch};
+        cuuint64_t dims[4] = {(cuuint64_t)kc, (cuuint64_t)g.W, (cuuint64_t)g.H, (cuuint64_t)g.batch};
         cuuint64_t strides[3] = {(cuuint64_t)g.sw * 4, (cuuint64_t)g.sh * 4, (cuuint64_t)g.sn * 4};
         cuuint32_t bx[4] = {(cuuint32_t)BLOCK_K, (cuuint32_t)(box.bw * g.stride), (cuuint32_t)(box.bh * g.stride),
                             (cuuint32_t)box.bn};
@@ -542,8 +582,8 @@ void gemm_tc(nb_handle_s *h, const GemmArgs &a, bool three_pass) {
         encode(h, &p.tm_a, a.a, 4, dims, strides, bx, es);
     }
     {   // B: dims {Kc, N, taps}
-        cuuint64_t dims[3] = {(cuuint64_t)a.Kc, (cuuint64_t)a.N, (cuuint64_t)taps};
-        cuuint64_t strides[2] = {(cuuint64_t)a.ldb * 4, (cuuint64_t)a.ldb * 4 * (cuuint64_t)a.N};
+        cuuint64_t dims[3] = {(cuuint64_t)kc, (cuuint64_t)a.N, (cuuint64_t)(S > 1 ? S : taps)};
+        cuuint64_t strides[2] = {(cuuint64_t)a.ldb * 4, S > 1 ? (cuuint64_t)kc * 4 : (cuuint64_t)a.ldb * 4 * (cuuint64_t)a.N};
         cuuint32_t bx[3] = {(cuuint32_t)BLOCK_K, (cuuint32_t)block_n, 1};
         cuuint32_t es[3] = {1, 1, 1};
         encode(h, &p.tm_b, a.b, 3, dims, strides, bx, es);

@@ -99,11 +99,10 @@ struct GemmArgs {
     bool a_is_conv = false;     // false: plain [M,K] with row stride lda
     long lda = 0;
     ConvGeom g;                 // used when a_is_conv
-    // tensor-core path only: build A in shared memory from the strided tensor described by g instead
-    // of loading it by TMA.  Entry kk of the table (Kc entries, Kc % 32 == 0) is
-    // {element offset of (c, kh-pad, kw-pad), ((kh-pad) & 0xffff) | (kw-pad) << 16}; the B operand is then
-    // a plain [N][Kc] matrix.
-    const void *gather_table = nullptr;
+    // tensor-core path only: build A in shared memory from the strided tensor described by g (any
+    // channel count, any strides) instead of loading it by TMA.  Column kk of A is (kh, kw, c) with c
+    // fastest, Kc = k*k*C rounded up to a multiple of 32; B is then a plain [N][Kc] matrix.
+    bool a_gather = false;
     // B operand: [taps][N][Kc] (taps = ksize*ksize, Kc = channels per tap, row stride ldb)
     const float *b = nullptr;       // operand used by the TF32 / FP32 paths
     const float *b_lo = nullptr;    // low-order split of B for the 3xTF32 path
@@ -121,6 +120,9 @@ struct GemmArgs {
     long ldy = 0;
     // tensor-core conv only: write the 2x2 stride-2 max-pooled output [B][OH/2][OW/2][N] here INSTEAD of y
     float *y_pool = nullptr;
+    // plain matrices only: contract K in `split_k` independent slices; slice s writes y + s*M*ldy
+    // (y must hold split_k * M * ldy floats; the caller reduces the slices and applies the epilogue)
+    int split_k = 1;
     double algo_flops = 0;          // algorithmic FLOPs of this launch for profiling (0: 2*M*N*Kc*taps)
 };
 
@@ -158,6 +160,9 @@ void launch_weight_relayout(nb_handle_s *h, const float *w_oihw, float *dst, int
 void launch_weight_pack(nb_handle_s *h, const float *w_oihw, float *dst, int F, int C, int k, int Kpad);
 // FC weights whose columns index (c,h,w) -> columns indexing (h,w,c)
 void launch_fc_permute(nb_handle_s *h, const float *w, float *dst, int out, int C, int H, int W);
+// sum of S slices [S][M][N] + folded scale/shift + activation (+ TF32 rounding) -> y [M][N]
+void launch_splitk_reduce(nb_handle_s *h, const float *ws, int S, int M, int N, const float *scale, const float *shift,
+                          int act, bool round_tf32, float *y);
 // LSTM cell: z [B,4H] (gate blocks i,f,g,o) -> c_t, h_t (+ TF32-rounded copy of h_t)
 void launch_lstm_cell(nb_handle_s *h, const float *z, const float *c_prev, float *c_out, float *h_out,
                       float *h_round, int B, int H);

@@ -2,6 +2,7 @@
 // layer's _forward_() would call.
 #include "plans.h"
 
+#include <algorithm>
 #include <cmath>
 #include <cstring>
 
@@ -65,7 +66,7 @@ ConvPlan::ConvPlan(nb_handle_s *hh, const nb_conv2d_desc_t &desc) : nb_plan_s(NB
     Cp = (d.channels + 3) / 4 * 4;
     const int K = d.channels * d.size * d.size;
     Kpad = (K + 31) / 32 * 32;
-    pack_ok = (Cp != d.channels || d.channels < 32) && Kpad <= 2048;
+    pack_ok = (Cp != d.channels || d.channels < 32) && Kpad <= 384;    // the gather table lives in the kernel parameters
 }
 
 void ConvPlan::set_weights(const float *weight, const float *bias, const float *g, const float *m, const float *v,
@@ -131,27 +132,8 @@ void ConvPlan::forward(const float *x, float *y, const ForwardOpts &o) {
         } else {
             g.sw = 1; g.sh = d.width; g.sc = (long)d.height * d.width; g.sn = (long)d.channels * d.height * d.width;
         }
-        // column kk = (kh,kw,c) -> where to read it, relative to the pixel's origin (oh*stride, ow*stride)
-        DeviceBuffer &tab = gather_tab[o.x_nhwc ? 1 : 0];
-        if (!tab.p) {
-            std::vector<int> host((size_t)2 * Kpad);
-            const int K = d.channels * d.size * d.size;
-            for (int kk = 0; kk < Kpad; kk++) {
-                int off = 0, dh = 30000, dw = 0;        // padding columns: a row offset that is never inside the image
-                if (kk < K) {
-                    const int tap = kk / d.channels, c = kk - tap * d.channels;
-                    dh = tap / d.size - d.padding; dw = tap % d.size - d.padding;
-                    off = (int)(c * g.sc + dh * g.sh + dw * g.sw);
-                }
-                host[2 * kk] = off;
-                host[2 * kk + 1] = (dh & 0xffff) | (dw << 16);
-            }
-            tab.alloc((size_t)2 * Kpad);
-            NB_CHECK_CUDA(cudaMemcpyAsync(tab.p, host.data(), host.size() * sizeof(int), cudaMemcpyHostToDevice, h->stream));
-            NB_CHECK_CUDA(cudaStreamSynchronize(h->stream));
-        }
         GemmArgs pa;
-        pa.a = x; pa.a_is_conv = true; pa.g = g; pa.gather_table = tab.p;
+        pa.a = x; pa.a_is_conv = true; pa.g = g; pa.a_gather = true;
         pa.ldb = Kpad; pa.M = (int)M; pa.N = d.filters; pa.Kc = Kpad;
         pa.scale = has_scale ? scale.p : nullptr; pa.shift = shift.p; pa.act = d.activation;
         pa.round_out_tf32 = o.round_out; pa.addend = o.addend; pa.ld_addend = d.filters;
@@ -303,9 +285,32 @@ void FcPlan::forward(const float *x, float *y, const ForwardOpts &o, int rows) {
     if (pth == PATH_SIMT) {
         a.b = w.exact.p;
         gemm_simt(h, a);
+        return;
+    }
+    w.ensure_split(h);
+    a.b = w.hi.p; a.b_lo = w.lo.p;
+    // Few rows and a long contraction (weight streaming): split K so that every SM pulls weights.
+    int S = 1;
+    if (pth == PATH_TC && !o.addend && (d.outputs % 4) == 0 && d.inputs >= 2048) {
+        const int kblocks = d.inputs / 32;
+        // chosen from K and N only, never from the batch: a batch and its slices add in the same order
+        const long tiles = (d.outputs + 127) / 128;
+        const int want = (int)std::min<long>(16, (2L * h->sm_count) / std::max<long>(1, tiles));
+        if ((d.inputs % 32) == 0)
+            for (int s = want; s >= 2; s--)
+                if (kblocks % s == 0 && kblocks / s >= 8) { S = s; break; }
+    }
+    if (S > 1) {
+        const size_t need = (size_t)S * M * d.outputs;
+        if (split_ws.n < need) split_ws.alloc(need);
+        GemmArgs sa = a;
+        sa.split_k = S;
+        sa.scale = nullptr; sa.shift = nullptr; sa.act = NB_ACT_LINEAR; sa.round_out_tf32 = false;
+        sa.y = split_ws.p; sa.ldy = d.outputs;
+        sa.algo_flops = 2.0 * (double)M * d.outputs * d.inputs;
+        gemm_tc(h, sa, false);
+        launch_splitk_reduce(h, split_ws.p, S, M, d.outputs, a.scale, a.shift, d.activation, o.round_out, y);
     } else {
-        w.ensure_split(h);
-        a.b = w.hi.p; a.b_lo = w.lo.p;
         gemm_tc(h, a, pth == PATH_TC3);
     }
 }

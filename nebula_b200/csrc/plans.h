@@ -58,7 +58,6 @@ struct ConvPlan : nb_plan_s {
     bool pack_ok = false;
     int Kpad = 0;
     WeightSet wp;                   // [F][Kpad], column = (kh,kw,c)
-    DeviceBuffer gather_tab[2];     // column -> input offset table for NCHW [0] and NHWC [1] inputs
     DeviceBuffer scale, shift;
     bool has_scale = false, ready = false;
     DeviceBuffer x_scratch, y_scratch;
@@ -76,7 +75,7 @@ struct FcPlan : nb_plan_s {
     WeightSet w;                    // [out][in]
     DeviceBuffer scale, shift;
     bool has_scale = false, ready = false;
-    DeviceBuffer x_scratch;
+    DeviceBuffer x_scratch, split_ws;
     // when the input is an NHWC activation, columns are permuted (c,h,w) -> (h,w,c)
     int perm_c = 0, perm_h = 0, perm_w = 0;
     FcPlan(nb_handle_s *h, const nb_fc_desc_t &desc);

@@ -60,6 +60,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// try_wait that lets the hardware park the thread (up to `ns`) until the phase completes, so a
+// waiting role does not take issue slots from the warps that share its scheduler
+__device__ __forceinline__ bool mbar_try_wait_parked(uint64_t *bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
+}
 // Bounded wait.  Returns false when the CTA is aborting (this wait or another ran out).
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -67,7 +80,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
     for (;;) {
 #pragma unroll 1
         for (int i = 0; i < 32; i++)
-            if (mbar_try_wait(bar, parity)) return true;
+            if (mbar_try_wait_parked(bar, parity, 20000u)) return true;
         if (*abort_flag) return false;
         if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
             *abort_flag = 1;

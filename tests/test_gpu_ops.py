@@ -84,7 +84,8 @@ def test_conv2d_nhwc_layout(handle, mode):
 
 FC_CASES = [(1, 32, 8, False, "linear"), (16, 256, 100, False, "relu"), (128, 512, 256, True, "leaky"),
             (33, 200, 77, False, "logistic"), (7, 50, 19, True, "tanh"), (256, 1024, 1000, False, "linear"),
-            (200, 96, 513, False, "relu")]
+            (200, 96, 513, False, "relu"),
+            (32, 4096, 1000, False, "relu"), (64, 8192, 512, True, "leaky")]      # long K, few rows: split-K path
 
 
 @pytest.mark.parametrize("mode", MODES)
