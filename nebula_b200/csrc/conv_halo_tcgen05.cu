@@ -139,16 +139,17 @@ __global__ void __launch_bounds__(320, 1) conv3x3_halo_tcgen05_kernel(const __gr
                     for (int tap = 0; tap < 9; tap++) {
                         if (!(ok = mbar_wait(&b_full[sb], pb, abort_flag, p.status))) break;
                         tc_fence_after();
-                        const uint32_t b_base = smem_u32(b_ring + sb * C::B_BYTES);
+                        const uint32_t b_lo = smem_desc_lo(smem_u32(b_ring + sb * C::B_BYTES));
                         const int kh = tap / 3, kw = tap - kh * 3;
-                        const uint32_t a_tap = a_base + (uint32_t)((kh * p.wt + kw) * 128);
-                        for (int hf = 0; hf < p.halves; hf++) {
+                        const uint32_t a_lo = smem_desc_lo(a_base + (uint32_t)((kh * p.wt + kw) * 128));
 #pragma unroll
-                            for (int k = 0; k < BLOCK_K / UMMA_K; k++) {
-                                const uint32_t koff = k * UMMA_K * 4;
-                                umma_tf32(d_tmem + (uint32_t)(hf * BLOCK_N), make_smem_desc(a_tap + hf * (BLOCK_M * 128) + koff),
-                                          make_smem_desc(b_base + koff), idesc, (cb | tap | k) != 0);
-                            }
+                        for (int k = 0; k < BLOCK_K / UMMA_K; k++)      // +32 bytes per K step = +2 in the descriptor
+                            umma_tf32(d_tmem, smem_desc(a_lo + 2 * k), smem_desc(b_lo + 2 * k), idesc, (cb | tap | k) != 0);
+                        if (p.halves == 2) {
+#pragma unroll
+                            for (int k = 0; k < BLOCK_K / UMMA_K; k++)  // second half: 128 rows = 16 KiB further on
+                                umma_tf32(d_tmem + BLOCK_N, smem_desc(a_lo + (BLOCK_M * 128 >> 4) + 2 * k), smem_desc(b_lo + 2 * k),
+                                          idesc, (cb | tap | k) != 0);
                         }
                         umma_commit(&b_empty[sb]);
                         if (++sb == B_RING) { sb = 0; pb ^= 1; }
@@ -195,6 +196,7 @@ __global__ void __launch_bounds__(320, 1) conv3x3_halo_tcgen05_kernel(const __gr
                 rw.srow = in_box ? lh * p.bw + jw : -1;
                 rw.row_ok = in_box && ow < p.OW && oh < p.OH;
                 rw.grow = ((long)n * p.OH + oh) * p.OW + ow;
+                rw.arow = addend_row(p.e, rw.row_ok, rw.grow, n, oh, ow);
                 const EpiBox bx{p.bw, p.rows_half, 1, tw * p.bw, th * p.bh + hf * p.rows_half, n};
                 uint32_t v[32];
                 tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * acc_cols + hf * BLOCK_N + chunk * 32), v);
@@ -256,7 +258,7 @@ bool conv_halo_supported(const nb_handle_s *h, const GemmArgs &a) {
     if (a.Kc < 32 || a.Kc > 128 || (a.Kc % 4) || (a.ldb % 4) || (a.N % 4)) return false;
     if ((g.sw % 4) || (g.sh % 4) || (g.sn % 4) || !aligned16(a.a) || !aligned16(a.b)) return false;
     if (g.OW < 14 || g.OH < 8) return false;
-    if (a.addend) return false;
+    if (a.addend && (a.res_stride <= 0 || (a.ld_addend % 4) || !aligned16(a.addend))) return false;
     if (a.y_pool ? ((g.OW | g.OH) & 1) || !aligned16(a.y_pool) : (!a.y || !aligned16(a.y) || (a.ldy % 4))) return false;
     return true;
 }
@@ -279,7 +281,9 @@ void conv_halo_tc(nb_handle_s *h, const GemmArgs &a) {
     const int block_n = a.N > 64 ? 128 : 64;
     p.n_tiles = (a.N + block_n - 1) / block_n;
     p.halo_bytes = BLOCK_K * 4 * p.wt * (p.bh + 2);
-    p.e.scale = a.scale; p.e.shift = a.shift; p.e.addend = nullptr; p.e.ld_addend = 0; p.e.addend_vec = 0;
+    p.e.scale = a.scale; p.e.shift = a.shift; p.e.addend = a.addend; p.e.ld_addend = a.ld_addend;
+    p.e.addend_vec = a.addend ? 1 : 0; p.e.addend_cols = a.addend ? a.res_c : 0;
+    p.e.res_stride = a.addend ? a.res_stride : 0; p.e.res_h = a.res_h; p.e.res_w = a.res_w;
     p.e.act = a.act; p.e.round_out = a.round_out_tf32 ? 1 : 0;
     p.e.y = a.y; p.e.ldy = a.ldy; p.e.tma_store = a.y_pool ? 0 : 1; p.e.pool = a.y_pool ? 1 : 0; p.e.N = a.N;
     p.status = h->d_status;

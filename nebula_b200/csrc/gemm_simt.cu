@@ -108,6 +108,7 @@ __global__ void __launch_bounds__(256) gemm_fp32_simt_kernel(const SimtParams p)
 }  // namespace
 
 void gemm_simt(nb_handle_s *h, const GemmArgs &a) {
+    if (a.addend && a.res_stride > 0) throw Error(NB_ERR_UNSUPPORTED, "the CUDA-core path takes no fused residual");
     SimtParams p;
     p.a = a.a; p.b = a.b;
     if (a.a_is_conv) {

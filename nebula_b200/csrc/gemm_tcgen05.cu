@@ -196,15 +196,13 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
                     if (!(ok = mbar_wait(ready, phase, abort_flag, p.status))) break;
                     tc_fence_after();
                     const uint32_t sa = smem_u32(smem + stage * C::STAGE_BYTES);
-                    const uint32_t sb = sa + A_STAGE_BYTES;
+                    const uint32_t a_lo = smem_desc_lo(sa), b_lo = smem_desc_lo(sa + A_STAGE_BYTES);
 #pragma unroll
-                    for (int k = 0; k < BLOCK_K / UMMA_K; k++) {
-                        const uint32_t koff = k * UMMA_K * 4;
-                        const uint64_t da = make_smem_desc(sa + koff);
-                        const uint64_t db = make_smem_desc(sb + koff);
+                    for (int k = 0; k < BLOCK_K / UMMA_K; k++) {        // +32 bytes per K step = +2 in the descriptor
+                        const uint64_t da = smem_desc(a_lo + 2 * k), db = smem_desc(b_lo + 2 * k);
                         if (THREE) {
-                            const uint64_t da_lo = make_smem_desc(sb + C::B_STAGE_BYTES + koff);
-                            const uint64_t db_lo = make_smem_desc(sb + C::B_STAGE_BYTES + A_STAGE_BYTES + koff);
+                            const uint64_t da_lo = smem_desc(b_lo + (C::B_STAGE_BYTES >> 4) + 2 * k);
+                            const uint64_t db_lo = smem_desc(b_lo + ((C::B_STAGE_BYTES + A_STAGE_BYTES) >> 4) + 2 * k);
                             umma_tf32(d_tmem, da_lo, db, idesc, (kb_in_part | k) != 0);
                             umma_tf32(d_tmem, da, db_lo, idesc, 1);
                             umma_tf32(d_tmem, da, db, idesc, 1);
@@ -246,7 +244,7 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
             const int ow = tw * p.bw + rw, oh = th * p.bh + rh, n = tn * p.bn + rn;
             const bool row_ok = (rn < p.bn) && ow < p.OW && oh < p.OH && n < p.NB;
             const long row = ((long)n * p.OH + oh) * p.OW + ow;
-            const EpiRow erow{r, row, row_ok};
+            const EpiRow erow{r, row, row_ok, addend_row(p.e, row_ok, row, n, oh, ow)};
             const EpiBox ebox{p.bw, p.bh, p.bn, tw * p.bw, th * p.bh, tn * p.bn};
             if (!PROMOTE || p.parts == 1) {
                 if (!(ok = epilogue_all(mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status), bar_id))) break;
@@ -527,6 +525,8 @@ void gemm_tc(nb_handle_s *h, const GemmArgs &a, bool three_pass) {
     p.e.scale = a.scale; p.e.shift = a.shift; p.e.addend = a.addend; p.e.ld_addend = a.ld_addend;
     p.e.act = a.act; p.e.round_out = a.round_out_tf32 ? 1 : 0;
     p.e.addend_vec = a.addend && aligned16(a.addend) && (a.ld_addend % 4) == 0;
+    p.e.addend_cols = a.addend ? (a.res_stride > 0 ? a.res_c : a.N) : 0;
+    p.e.res_stride = a.addend ? a.res_stride : 0; p.e.res_h = a.res_h; p.e.res_w = a.res_w;
     p.e.y = a.y; p.e.ldy = a.ldy;
     p.e.tma_store = a.y && aligned16(a.y) && (a.ldy % 4) == 0;
     p.e.pool = pool ? 1 : 0;

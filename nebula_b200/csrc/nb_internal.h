@@ -112,8 +112,11 @@ struct GemmArgs {
     // epilogue
     const float *scale = nullptr;   // may be null (=1)
     const float *shift = nullptr;   // may be null (=0)
-    const float *addend = nullptr;  // may be null; same indexing as y
+    const float *addend = nullptr;  // may be null; same indexing as y unless res_stride > 0
     long ld_addend = 0;
+    // residual form of the addend (tensor-core conv kernels): NHWC tensor [batch][res_h][res_w][ld_addend] of
+    // which output pixel (n,oh,ow) takes channels [0,res_c) of pixel (n, oh*res_stride, ow*res_stride)
+    int res_stride = 0, res_c = 0, res_h = 0, res_w = 0;
     int act = NB_ACT_LINEAR;
     bool round_out_tf32 = false;    // store RN(TF32) values (the consumer is a TF32 contraction)
     float *y = nullptr;

@@ -308,6 +308,25 @@ void nb_network_s::forward(const float *input) {
                         continue;
                     }
                 }
+                // conv (linear) -> shortcut: the residual add and the shortcut's activation run in the conv epilogue
+                if (fuse && !referenced && i + 1 < n && layers[i + 1]->type == LT_SHORTCUT) {
+                    NetLayer &sl = *layers[i + 1];
+                    const nb_shortcut_desc_t &sd = sl.shortcut;
+                    NetLayer &cl = *layers[sl.conn];
+                    if (cl.materialised && sl.conn != i && l.conv->can_fuse_shortcut(sd.conn_channels, sd.conn_height, sd.conn_width)) {
+                        const bool sc_round = consumer_is_tf32(i + 1);
+                        o.round_out = sc_round;
+                        o.residual = cl.out_ptr;
+                        o.res_c = sd.conn_channels; o.res_h = sd.conn_height; o.res_w = sd.conn_width;
+                        o.res_act = sd.activation;
+                        l.conv->forward(cur, sl.out_ptr, o);
+                        l.materialised = false;
+                        sl.out_is_rounded = sc_round;
+                        cur = sl.out_ptr; cur_nhwc = true; cur_rounded = sc_round; cur_round = nullptr;
+                        i++;
+                        continue;
+                    }
+                }
                 l.conv->forward(cur, l.out_ptr, o);
                 break;
             }

@@ -110,6 +110,13 @@ bool ConvPlan::can_fuse_pool() const {
     return (pth == PATH_TC || pth == PATH_TC3) && !(OH & 1) && !(OW & 1) && (d.filters % 4) == 0 && OH >= 2 && OW >= 2;
 }
 
+bool ConvPlan::can_fuse_shortcut(int conn_c, int conn_h, int conn_w) const {
+    const GemmPath pth = path(ForwardOpts());
+    // sample == 1 (the connection is not smaller than this layer's output), linear conv, aligned channel rows
+    return (pth == PATH_TC || pth == PATH_TC3) && d.activation == NB_ACT_LINEAR && conn_w >= OW && conn_h >= OH &&
+           (conn_c % 4) == 0 && (d.filters % 4) == 0;
+}
+
 void ConvPlan::forward(const float *x, float *y, const ForwardOpts &o) {
     if (!ready) throw Error(NB_ERR_NO_WEIGHTS, "conv: forward before set_weights");
     NB_REQUIRE(x && (y || o.pool_out), "conv: null tensor pointer");
@@ -191,6 +198,15 @@ void ConvPlan::forward(const float *x, float *y, const ForwardOpts &o) {
     }
     a.y = yo;
     a.ldy = d.filters;
+    if (o.residual) {
+        NB_REQUIRE(o.y_nhwc && pth != PATH_SIMT && !o.addend && !o.pool_out, "conv: fused shortcut needs the tensor-core path and NHWC output");
+        a.addend = o.residual;
+        a.ld_addend = o.res_c;
+        a.res_stride = std::max(1, o.res_w / OW);       // common/utils.cc:31
+        a.res_c = std::min(o.res_c, d.filters);
+        a.res_h = o.res_h; a.res_w = o.res_w;
+        a.act = o.res_act;
+    }
     if (o.pool_out) {
         NB_REQUIRE(o.y_nhwc && pth != PATH_SIMT, "conv: fused pooling needs the tensor-core path and NHWC output");
         a.y = nullptr;

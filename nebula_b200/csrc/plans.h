@@ -47,6 +47,10 @@ struct ForwardOpts {
     bool round_out = false;         // store TF32-rounded outputs (consumer is a TF32 contraction)
     const float *addend = nullptr;  // optional tensor added before the activation (same layout as y)
     float *pool_out = nullptr;      // conv: write only the 2x2/2 max-pooled NHWC output here (y is not written)
+    // conv (tensor-core path, NHWC): fuse the following shortcut layer -- add channels [0,min(C)) of this NHWC
+    // tensor (sub-sampled when it is spatially larger) and apply `res_act` instead of the conv's own (linear) activation
+    const float *residual = nullptr;
+    int res_c = 0, res_h = 0, res_w = 0, res_act = 0;
 };
 
 struct ConvPlan : nb_plan_s {
@@ -68,6 +72,7 @@ struct ConvPlan : nb_plan_s {
     GemmPath path(const ForwardOpts &o) const;
     // can the following 2x2 stride-2 max-pool be done in this layer's epilogue?
     bool can_fuse_pool() const;
+    bool can_fuse_shortcut(int conn_c, int conn_h, int conn_w) const;
 };
 
 struct FcPlan : nb_plan_s {

@@ -24,6 +24,11 @@ struct EpiParams {
     const float *scale, *shift, *addend;    // scale/shift readable up to the next multiple of 32 columns
     long ld_addend;
     int addend_vec;             // addend rows are 16-byte aligned
+    int addend_cols;            // columns the addend covers (a residual may have fewer channels than the output)
+    // residual mode (res_stride > 0): the addend is an NHWC tensor [NB][res_h][res_w][ld_addend] and output
+    // pixel (n,oh,ow) takes pixel (n, oh*res_stride, ow*res_stride) of it -- the reference's shortcut
+    // (common/utils.cc:28-60) with sample == 1; otherwise the addend has the output's own row indexing
+    int res_stride, res_h, res_w;
     int act, round_out;
     float *y;
     long ldy;
@@ -33,7 +38,16 @@ struct EpiParams {
 };
 // Per thread: its row of the staging slab (-1: this accumulator row is not an output pixel), the
 // output pixel index for plain stores / addend reads, and whether that pixel exists.
-struct EpiRow { int srow; long grow; bool row_ok; };
+struct EpiRow { int srow; long grow; bool row_ok; const float *arow; };
+
+// This pixel's addend row (nullptr: nothing to add).
+__device__ __forceinline__ const float *addend_row(const EpiParams &e, bool row_ok, long grow, int n, int oh, int ow) {
+    if (!e.addend || !row_ok) return nullptr;
+    if (e.res_stride == 0) return e.addend + grow * e.ld_addend;
+    const int ih = oh * e.res_stride, iw = ow * e.res_stride;
+    if (oh >= e.res_h || ow >= e.res_w || ih >= e.res_h || iw >= e.res_w) return nullptr;
+    return e.addend + (((long)n * e.res_h + ih) * e.res_w + iw) * e.ld_addend;
+}
 // The pixel box one slab covers and its origin in output coordinates.
 struct EpiBox { int bw, bh, bn, ow0, oh0, n0; };
 
@@ -158,6 +172,13 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
     return d;
 }
 
+// The same descriptor split in halves, for the MMA issue loop: the upper word is a constant, the lower
+// word is (start >> 4) | LBO, so stepping the start address by b bytes is `lo += b >> 4` (shared-memory
+// addresses stay below 2^18, so the 14-bit field never carries).
+constexpr uint32_t SMEM_DESC_HI = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t smem_desc_lo(uint32_t smem_addr) { return ((smem_addr >> 4) & 0x3FFF) | (1u << 16); }
+__device__ __forceinline__ uint64_t smem_desc(uint32_t lo) { return ((uint64_t)SMEM_DESC_HI << 32) | lo; }
+
 // Instruction descriptor for kind::tf32: D=f32 (bits 4-5 = 1), A=B=tf32 (bits
 // 7-9, 10-12 = 2), both K-major (bits 15,16 = 0), N>>3 at bit 17, M>>4 at bit 24.
 __host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
@@ -222,9 +243,9 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams &e, const CUtenso
             v[j + 3] = __float_as_uint(__uint_as_float(v[j + 3]) + sh.w);
         }
     }
-    if (e.addend && rw.row_ok) {
-        const float *arow = e.addend + rw.grow * e.ld_addend + col0;
-        if (full_cols && e.addend_vec) {
+    if (rw.arow && col0 < e.addend_cols) {
+        const float *arow = rw.arow + col0;
+        if (col0 + 32 <= e.addend_cols && e.addend_vec) {
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {
                 const float4 ad = *reinterpret_cast<const float4 *>(arow + j);
@@ -236,7 +257,7 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams &e, const CUtenso
         } else {
 #pragma unroll
             for (int j = 0; j < 32; j++)
-                if (col0 + j < e.N) v[j] = __float_as_uint(__uint_as_float(v[j]) + arow[j]);
+                if (col0 + j < e.addend_cols) v[j] = __float_as_uint(__uint_as_float(v[j]) + arow[j]);
         }
     }
     // activation: the common ones inline, the rest through one out-of-line call per value

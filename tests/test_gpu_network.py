@@ -76,21 +76,25 @@ def test_alexnet_full_size_two_images(handle):
 
 
 @pytest.mark.parametrize("mode", ["tf32", "tf32x3"])
-@pytest.mark.parametrize("name", ["tiny_vgg", "toy", "mid_vgg"])
-def test_fused_pooling_is_bit_identical(handle, name, mode):
-    """conv + 2x2/2 max-pool in one kernel gives exactly what the two kernels give."""
+@pytest.mark.parametrize("name", ["tiny_vgg", "toy", "mid_vgg", "tiny_resnet"])
+def test_fused_layers_are_bit_identical(handle, name, mode):
+    """conv + 2x2/2 max-pool and conv + shortcut run as one kernel give exactly what the separate
+    kernels give; only the fused convolutions' own outputs are no longer kept."""
     from nebula_b200 import api
     wl = NETS[name](batch=5)
     a, w, x = _run(handle, wl, mode, fusion=False)
     b, _, _ = _run(handle, wl, mode, fusion=True)
     assert np.array_equal(a.logits(), b.logits())
-    pools = [i for i in range(a.num_layers) if a.layer_info(i)["type"] == "maxpool"]
-    assert pools
-    for i in pools:
-        assert np.array_equal(a.layer_output(i, 5), b.layer_output(i, 5)), f"pool layer {i}"
-    if name == "tiny_vgg":
-        with pytest.raises(api.NebulaError):        # the fused convolution's own output is not kept
-            b.layer_output(pools[0] - 1, 5)
+    fused = 0
+    for i in range(a.num_layers):
+        try:
+            got = b.layer_output(i, 5)
+        except api.NebulaError as e:
+            assert e.code == 3 and a.layer_info(i)["type"] == "convolutional"
+            fused += 1
+            continue
+        assert np.array_equal(a.layer_output(i, 5), got), f"layer {i} ({a.layer_info(i)['type']})"
+    assert fused > 0
     a.close()
     b.close()
 
