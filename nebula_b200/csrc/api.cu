@@ -85,6 +85,8 @@ int nb_destroy(nb_handle_t h) {
     cudaSetDevice(h->device);
     cudaStreamSynchronize(h->stream);
     if (h->d_status) cudaFree(h->d_status);
+    for (auto e : h->event_pool) cudaEventDestroy(e);
+    for (auto &t : h->timed) { cudaEventDestroy(t.start); cudaEventDestroy(t.stop); }
     delete h;
     return NB_OK;
 }
@@ -132,7 +134,7 @@ int nb_launch_count(nb_handle_t h, unsigned long long *count) {
 
 int nb_profile_begin(nb_handle_t h) {
     if (!h) return NB_ERR_INVALID_ARG;
-    for (auto &t : h->timed) { cudaEventDestroy(t.start); cudaEventDestroy(t.stop); }
+    for (auto &t : h->timed) { h->event_pool.push_back(t.start); h->event_pool.push_back(t.stop); }
     h->timed.clear();
     h->profiling = true;
     return NB_OK;
@@ -150,7 +152,7 @@ int nb_profile_end(nb_handle_t h, nb_profile_t *r) {
             if (t.kind == 0) { r->tc_ms += ms; r->tc_flops += t.flops; r->tc_launches++; }
             else if (t.kind == 2) { r->halo_ms += ms; r->halo_flops += t.flops; r->halo_launches++; }
             else { r->simt_ms += ms; r->simt_flops += t.flops; r->simt_launches++; }
-            cudaEventDestroy(t.start); cudaEventDestroy(t.stop);
+            h->event_pool.push_back(t.start); h->event_pool.push_back(t.stop);
         }
         h->timed.clear();
     });

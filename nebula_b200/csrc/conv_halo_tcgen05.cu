@@ -224,11 +224,8 @@ __global__ void __launch_bounds__(320, 1) conv3x3_halo_tcgen05_kernel(const __gr
 
 void encode(nb_handle_s *h, CUtensorMap *tm, const void *base, int rank, const cuuint64_t *dims,
             const cuuint64_t *strides_bytes, const cuuint32_t *box) {
-    cuuint32_t es[5] = {1, 1, 1, 1, 1};
-    CUresult r = h->encode_tiled(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, const_cast<void *>(base), dims,
-                                 strides_bytes, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                                 CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) throw Error(NB_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+    const cuuint32_t es[5] = {1, 1, 1, 1, 1};
+    encode_tensor_map(h, tm, base, rank, dims, strides_bytes, box, es);
 }
 
 template <int BLOCK_N>

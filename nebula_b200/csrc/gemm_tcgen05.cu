@@ -436,11 +436,7 @@ Box choose_box(int OW, int OH, int NB, int stride, bool even) {
 
 void encode(nb_handle_s *h, CUtensorMap *tm, const void *base, int rank, const cuuint64_t *dims,
             const cuuint64_t *strides_bytes, const cuuint32_t *box, const cuuint32_t *elem_strides) {
-    CUresult r = h->encode_tiled(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, const_cast<void *>(base), dims,
-                                 strides_bytes, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) throw Error(NB_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+    encode_tensor_map(h, tm, base, rank, dims, strides_bytes, box, elem_strides);
 }
 
 template <int BLOCK_N, bool THREE, bool PROMOTE>
@@ -463,6 +459,27 @@ void launch(nb_handle_s *h, const TcParams &p) {
 inline bool aligned16(const void *p) { return ((uintptr_t)p & 15) == 0; }
 
 }  // namespace
+
+void encode_tensor_map(nb_handle_s *h, CUtensorMap *tm, const void *base, int rank, const cuuint64_t *dims,
+                       const cuuint64_t *strides_bytes, const cuuint32_t *box, const cuuint32_t *elem_strides) {
+    std::string key;
+    key.reserve(160);
+    key.append((const char *)&base, sizeof base);
+    key.append((const char *)&rank, sizeof rank);
+    key.append((const char *)dims, sizeof(cuuint64_t) * rank);
+    key.append((const char *)strides_bytes, sizeof(cuuint64_t) * (rank - 1));
+    key.append((const char *)box, sizeof(cuuint32_t) * rank);
+    key.append((const char *)elem_strides, sizeof(cuuint32_t) * rank);
+    auto it = h->tensor_maps.find(key);
+    if (it != h->tensor_maps.end()) { *tm = it->second; return; }
+    CUresult r = h->encode_tiled(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, const_cast<void *>(base), dims,
+                                 strides_bytes, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) throw Error(NB_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+    if (h->tensor_maps.size() > 8192) h->tensor_maps.clear();
+    h->tensor_maps.emplace(std::move(key), *tm);
+}
 
 bool gemm_tc_supported(const nb_handle_s *h, const GemmArgs &a) {
     if (!h->encode_tiled || h->cc_major != 10) return false;

@@ -7,6 +7,7 @@
 
 #include <stdexcept>
 #include <string>
+#include <unordered_map>
 #include <vector>
 
 #include "../../include/nebula_b200.h"
@@ -55,6 +56,10 @@ struct nb_handle_s {
     struct Timed { cudaEvent_t start, stop; double flops; int kind; };
     bool profiling = false;
     std::vector<Timed> timed;
+    std::vector<cudaEvent_t> event_pool;    // events are re-used across profiling windows
+    // encoded TMA descriptors, keyed by every argument of the encode call (layers keep their buffers, so a
+    // network's forward pass re-uses the same few dozen maps on every call)
+    std::unordered_map<std::string, CUtensorMap> tensor_maps;
 };
 
 namespace nb {
@@ -183,7 +188,11 @@ struct ProfileScope {
     ProfileScope(nb_handle_s *hh, int kind, double flops) : h(hh), on(hh->profiling) {
         if (!on) return;
         t.kind = kind; t.flops = flops;
-        cudaEventCreate(&t.start); cudaEventCreate(&t.stop);
+        auto take = [&](cudaEvent_t &e) {
+            if (h->event_pool.empty()) cudaEventCreate(&e);
+            else { e = h->event_pool.back(); h->event_pool.pop_back(); }
+        };
+        take(t.start); take(t.stop);
         cudaEventRecord(t.start, h->stream);
     }
     ~ProfileScope() {
@@ -192,6 +201,10 @@ struct ProfileScope {
         h->timed.push_back(t);
     }
 };
+
+// fp32, 128-byte swizzle, zero fill: the one kind of tensor map the kernels use (cached per handle)
+void encode_tensor_map(nb_handle_s *h, CUtensorMap *tm, const void *base, int rank, const cuuint64_t *dims,
+                       const cuuint64_t *strides_bytes, const cuuint32_t *box, const cuuint32_t *elem_strides);
 
 inline void count_launch(nb_handle_s *h, int n = 1) { h->launches += (unsigned long long)n; }
 void check_launch(const char *what);
