@@ -61,7 +61,9 @@ struct TcParams {
     int num_k_blocks;           // ksize*ksize*c_blocks
     int m_tiles, n_tiles;
     int tx_bytes_a;             // bytes one A box load delivers
-    int b_from_th;              // split-K: the weight tile's third coordinate is the tile's row index th
+    // split-K: a tile is (m_tile, n_tile, split); split s runs K blocks [s*kb_per_split, (s+1)*kb_per_split)
+    // and stores into slab s of y (batch coordinate n + s*NB): y then holds k_splits partial tensors
+    int k_splits, kb_per_split;
     // The tensor core's fp32 accumulator rounds toward zero at every K=8 step (a bias that grows with K).
     // After every kb_per_part K blocks the partial sums are promoted to registers (round-to-nearest adds)
     // and the TMEM accumulator restarts; parts = number of such partial sums per tile (1: no promotion).
@@ -111,7 +113,7 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int total_tiles = p.m_tiles * p.n_tiles;
+    const int total_tiles = p.m_tiles * p.n_tiles * p.k_splits;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
@@ -144,14 +146,15 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
             uint32_t phase = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const int m_tile = tile / p.n_tiles, n_tile = tile % p.n_tiles;
+                const int split = tile % p.k_splits, mn = tile / p.k_splits;
+                const int m_tile = mn / p.n_tiles, n_tile = mn % p.n_tiles;
                 const int tw = m_tile % p.tiles_w;
                 const int th = (m_tile / p.tiles_w) % p.tiles_h;
                 const int tn = m_tile / (p.tiles_w * p.tiles_h);
                 const int w0 = tw * p.bw * p.stride - p.pad;
                 const int h0 = th * p.bh * p.stride - p.pad;
                 const int n0 = tn * p.bn;
-                for (int kb = 0; kb < p.num_k_blocks; kb++) {
+                for (int kb = split * p.kb_per_split; kb < (split + 1) * p.kb_per_split; kb++) {
                     if (!(ok = mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status))) break;
                     const int tap = kb / p.c_blocks, cb = kb - tap * p.c_blocks;
                     const int kh = tap / p.ksize, kw = tap - kh * p.ksize;
@@ -159,7 +162,7 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
                     uint8_t *sb = sa + A_STAGE_BYTES;
                     mbar_expect_tx(&full[stage], (uint32_t)((p.gather ? 0 : p.tx_bytes_a) + C::B_STAGE_BYTES * (THREE ? 2 : 1)));
                     if (!p.gather) tma_load_4d(sa, &p.tm_a, &full[stage], cb * BLOCK_K, w0 + kw, h0 + kh, n0);
-                    tma_load_3d(sb, &p.tm_b, &full[stage], cb * BLOCK_K, n_tile * BLOCK_N, p.b_from_th ? th : tap);
+                    tma_load_3d(sb, &p.tm_b, &full[stage], cb * BLOCK_K, n_tile * BLOCK_N, tap);
                     if (THREE)
                         tma_load_3d(sb + C::B_STAGE_BYTES + A_STAGE_BYTES, &p.tm_b_lo, &full[stage], cb * BLOCK_K,
                                     n_tile * BLOCK_N, tap);
@@ -182,7 +185,7 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
                 tc_fence_after();
                 uint32_t d_tmem = tmem_base + (uint32_t)(acc * BLOCK_N);
                 int kb_in_part = 0;
-                for (int kb = 0; kb < p.num_k_blocks; kb++, kb_in_part++) {
+                for (int kb = 0; kb < p.kb_per_split; kb++, kb_in_part++) {
                     if (kb_in_part == p.kb_per_part) {
                         // hand this partial sum to the epilogue warps and restart in the other accumulator
                         umma_commit(&acc_full[acc]);
@@ -237,7 +240,8 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
         uint32_t acc_phase = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-            const int m_tile = tile / p.n_tiles, n_tile = tile % p.n_tiles;
+            const int split = tile % p.k_splits, mn = tile / p.k_splits;
+            const int m_tile = mn / p.n_tiles, n_tile = mn % p.n_tiles;
             const int tw = m_tile % p.tiles_w;
             const int th = (m_tile / p.tiles_w) % p.tiles_h;
             const int tn = m_tile / (p.tiles_w * p.tiles_h);
@@ -245,7 +249,7 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
             const bool row_ok = (rn < p.bn) && ow < p.OW && oh < p.OH && n < p.NB;
             const long row = ((long)n * p.OH + oh) * p.OW + ow;
             const EpiRow erow{r, row, row_ok, addend_row(p.e, row_ok, row, n, oh, ow)};
-            const EpiBox ebox{p.bw, p.bh, p.bn, tw * p.bw, th * p.bh, tn * p.bn};
+            const EpiBox ebox{p.bw, p.bh, p.bn, tw * p.bw, th * p.bh, tn * p.bn + split * p.NB};
             if (!PROMOTE || p.parts == 1) {
                 if (!(ok = epilogue_all(mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status), bar_id))) break;
                 tc_fence_after();
@@ -309,7 +313,7 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
         uint32_t phase = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-            const int m_tile = tile / p.n_tiles;
+            const int m_tile = tile / p.k_splits / p.n_tiles;
             const long m = (long)m_tile * BLOCK_M + t;
             const bool valid = m < p.gM;
             int ih0 = 0, iw0 = 0;
@@ -324,7 +328,7 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
             // does every tap of this pixel fall inside the image?  (true for all but border pixels)
             const int ihf = ih0 - p.gpad, iwf = iw0 - p.gpad;
             const bool interior = valid && ihf >= 0 && iwf >= 0 && ihf + p.gks <= p.gH && iwf + p.gks <= p.gW;
-            for (int kb = 0; kb < p.num_k_blocks; kb++) {
+            for (int kb = 0; kb < p.kb_per_split; kb++) {        // gather mode never splits K
                 if (!(ok = mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status))) break;
                 float4 *a_row = reinterpret_cast<float4 *>(smem + stage * C::STAGE_BYTES + t * 128);
                 float4 *a_lo_row = reinterpret_cast<float4 *>(smem + stage * C::STAGE_BYTES + A_STAGE_BYTES + C::B_STAGE_BYTES + t * 128);
@@ -372,7 +376,7 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
         uint32_t phase = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-            for (int kb = 0; kb < p.num_k_blocks; kb++) {
+            for (int kb = 0; kb < p.kb_per_split; kb++) {
                 if (!(ok = mbar_wait(&full[stage], phase, abort_flag, p.status))) break;
                 float4 *a = reinterpret_cast<float4 *>(smem + stage * C::STAGE_BYTES);
                 float4 *a_lo = reinterpret_cast<float4 *>(smem + stage * C::STAGE_BYTES + A_STAGE_BYTES + C::B_STAGE_BYTES);
@@ -414,15 +418,17 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
 struct Box { int bw, bh, bn; };
 
 // Chooses the (bw x bh x bn) pixel box (<= 128 rows) that wastes the fewest MMA rows.
-Box choose_box(int OW, int OH, int NB, int stride, bool even) {
+// bn_divides: the images of a box must not run past the batch (split-K slabs follow each other in y)
+Box choose_box(int OW, int OH, int NB, int stride, bool even, bool bn_divides) {
     Box best{1, 1, 1};
     double best_eff = -1;
     const int max_dim = 256 / std::max(1, stride);     // TMA box extent limit (elements traversed)
     for (int bw = 1; bw <= std::min({OW, 128, max_dim}); bw++) {
         const int rem = 128 / bw;
         for (int bh = 1; bh <= std::min({OH, rem, max_dim}); bh++) {
-            const int bn = std::min({NB, 128 / (bw * bh), 256});
+            int bn = std::min({NB, 128 / (bw * bh), 256});
             if (bn < 1) continue;
+            while (bn_divides && NB % bn) bn--;
             if (even && ((bw | bh) & 1)) continue;      // 2x2 pooling windows must not straddle tiles
             auto eff1 = [](int ext, int b) { return (double)ext / ((double)((ext + b - 1) / b) * b); };
             double eff = eff1(OW, bw) * eff1(OH, bh) * eff1(NB, bn) * (double)(bw * bh * bn) / 128.0;
@@ -513,20 +519,13 @@ void gemm_tc(nb_handle_s *h, const GemmArgs &a, bool three_pass) {
         g.ksize = 1; g.stride = 1; g.pad = 0;
         g.sc = 1; g.sw = a.lda; g.sh = (long)a.lda * a.M; g.sn = (long)a.lda * a.M;
     }
-    // Split-K (plain matrices only): split s contracts columns [s*kc, (s+1)*kc) and writes its own
-    // [M,N] slab of y.  Expressed through the same machinery as an "image" of height S whose row
-    // stride is kc elements; the weight tile's third coordinate is the split index.
-    const int S = (!a.a_is_conv && !gather && a.split_k > 1) ? a.split_k : 1;
-    const int kc = a.Kc / S;
-    if (S > 1) {
-        if (a.Kc % (S * BLOCK_K) || a.y_pool || a.addend || three_pass)
-            throw Error(NB_ERR_INVALID_ARG, "split-K needs K divisible by 32*splits and a plain epilogue");
-        g.C = kc; g.H = S; g.OH = S; g.sh = kc;
-    }
+    // Split-K: the K blocks (taps x channel slices) are divided among `split_k` tiles that each write their
+    // own slab of y ([split][batch][OH][OW][N]); the caller adds the slabs and applies the epilogue.
+    const int S = (!gather && a.split_k > 1) ? a.split_k : 1;
+    const int kc = a.Kc;
     const int taps = g.ksize * g.ksize;
     const bool pool = a.y_pool != nullptr;
-    Box box = choose_box(g.OW, g.OH, g.batch, g.stride, pool);
-    if (S > 1) box = Box{std::min(128, g.OW), 1, 1};
+    Box box = choose_box(g.OW, g.OH, g.batch, g.stride, pool, S > 1);
     p.bw = box.bw; p.bh = box.bh; p.bn = box.bn;
     p.tiles_w = (g.OW + box.bw - 1) / box.bw;
     p.tiles_h = (g.OH + box.bh - 1) / box.bh;
@@ -534,8 +533,11 @@ void gemm_tc(nb_handle_s *h, const GemmArgs &a, bool three_pass) {
     p.OW = g.OW; p.OH = g.OH; p.NB = g.batch;
     p.ksize = g.ksize; p.stride = g.stride; p.pad = g.pad;
     p.c_blocks = (kc + BLOCK_K - 1) / BLOCK_K;
-    p.b_from_th = S > 1 ? 1 : 0;
     p.num_k_blocks = taps * p.c_blocks;
+    if (S > 1 && (p.num_k_blocks % S || a.y_pool || a.addend || three_pass || a.scale || a.shift || a.act != NB_ACT_LINEAR))
+        throw Error(NB_ERR_INVALID_ARG, "split-K needs a number of K blocks divisible by the splits and a plain epilogue");
+    p.k_splits = S;
+    p.kb_per_split = p.num_k_blocks / S;
     p.m_tiles = p.tiles_w * p.tiles_h * p.tiles_n;
     p.e.N = a.N;
     p.tx_bytes_a = BLOCK_K * 4 * box.bw * box.bh * box.bn;
@@ -546,6 +548,7 @@ void gemm_tc(nb_handle_s *h, const GemmArgs &a, bool three_pass) {
     p.e.res_stride = a.addend ? a.res_stride : 0; p.e.res_h = a.res_h; p.e.res_w = a.res_w;
     p.e.y = a.y; p.e.ldy = a.ldy;
     p.e.tma_store = a.y && aligned16(a.y) && (a.ldy % 4) == 0;
+    if (S > 1 && !p.e.tma_store) throw Error(NB_ERR_INVALID_ARG, "split-K needs a 16-byte aligned output with ldy % 4 == 0");
     p.e.pool = pool ? 1 : 0;
     if (pool) {
         if (!a.a_is_conv || (g.OW & 1) || (g.OH & 1) || (a.N % 4) || !aligned16(a.y_pool) || a.addend)
@@ -559,19 +562,19 @@ void gemm_tc(nb_handle_s *h, const GemmArgs &a, bool three_pass) {
     // tile width in filters: widest tile that still gives every SM work
     // Promoted accumulation: always for 3xTF32 (its point is fp32-level agreement); in TF32 mode only for
     // very long contractions, where the accumulator's round-toward-zero bias (~K * 7.5e-9) nears TF32's own error.
-    const bool promote = three_pass || (long)p.num_k_blocks * BLOCK_K >= 8192;   // per split when K is split
+    const bool promote = three_pass || (long)p.kb_per_split * BLOCK_K >= 8192;   // per split when K is split
     int block_n = 256;
     if (three_pass || gather || promote) block_n = 128;
     while (block_n > 64) {
-        const long tiles = (long)p.m_tiles * ((a.N + block_n - 1) / block_n);
+        const long tiles = (long)p.m_tiles * S * ((a.N + block_n - 1) / block_n);
         if (a.N > block_n / 2 && tiles >= h->sm_count) break;
         if (a.N > block_n / 2 && (long)p.m_tiles * ((a.N + block_n / 2 - 1) / (block_n / 2)) > 2L * h->sm_count) break;
         block_n /= 2;
     }
     p.n_tiles = (a.N + block_n - 1) / block_n;
     // accumulation chains of at most 512 (TF32) / 128 (3xTF32) K elements in the tensor core
-    p.kb_per_part = !promote ? p.num_k_blocks : (three_pass ? 4 : 16);
-    p.parts = (p.num_k_blocks + p.kb_per_part - 1) / p.kb_per_part;
+    p.kb_per_part = !promote ? p.kb_per_split : (three_pass ? 4 : 16);
+    p.parts = (p.kb_per_split + p.kb_per_part - 1) / p.kb_per_part;
 
     p.gather = gather ? 1 : 0;
     if (gather) {
@@ -599,8 +602,8 @@ void gemm_tc(nb_handle_s *h, const GemmArgs &a, bool three_pass) {
         encode(h, &p.tm_a, a.a, 4, dims, strides, bx, es);
     }
     {   // B: dims {Kc, N, taps}
-        cuuint64_t dims[3] = {(cuuint64_t)kc, (cuuint64_t)a.N, (cuuint64_t)(S > 1 ? S : taps)};
-        cuuint64_t strides[2] = {(cuuint64_t)a.ldb * 4, S > 1 ? (cuuint64_t)kc * 4 : (cuuint64_t)a.ldb * 4 * (cuuint64_t)a.N};
+        cuuint64_t dims[3] = {(cuuint64_t)kc, (cuuint64_t)a.N, (cuuint64_t)taps};
+        cuuint64_t strides[2] = {(cuuint64_t)a.ldb * 4, (cuuint64_t)a.ldb * 4 * (cuuint64_t)a.N};
         cuuint32_t bx[3] = {(cuuint32_t)BLOCK_K, (cuuint32_t)block_n, 1};
         cuuint32_t es[3] = {1, 1, 1};
         encode(h, &p.tm_b, a.b, 3, dims, strides, bx, es);
@@ -608,7 +611,7 @@ void gemm_tc(nb_handle_s *h, const GemmArgs &a, bool three_pass) {
     }
 
     if (p.e.tma_store) {   // Y: dims {N, OW, OH, NB}; the same pixel box as A, 32 columns wide
-        cuuint64_t dims[4] = {(cuuint64_t)a.N, (cuuint64_t)g.OW, (cuuint64_t)g.OH, (cuuint64_t)g.batch};
+        cuuint64_t dims[4] = {(cuuint64_t)a.N, (cuuint64_t)g.OW, (cuuint64_t)g.OH, (cuuint64_t)g.batch * (cuuint64_t)S};
         cuuint64_t strides[3] = {(cuuint64_t)a.ldy * 4, (cuuint64_t)a.ldy * 4 * (cuuint64_t)g.OW,
                                  (cuuint64_t)a.ldy * 4 * (cuuint64_t)g.OW * (cuuint64_t)g.OH};
         cuuint32_t bx[4] = {32, (cuuint32_t)box.bw, (cuuint32_t)box.bh, (cuuint32_t)box.bn};

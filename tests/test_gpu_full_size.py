@@ -73,8 +73,9 @@ def test_lstm_benchmark_geometry_against_reference(handle):
 
 
 def test_vgg16_full_batch_equals_its_slices(handle):
-    """Size-independent property at the benchmark batch: rows of the b256 run are
-    bit-identical to the same images run as a batch of 8."""
+    """Size-independent property at the benchmark batch: rows of the b256 run are bit-identical
+    to the same images run as a batch of 8 (tile shapes change with the batch, the order of
+    additions inside an output element does not)."""
     import torch
     from nebula_b200 import api
     handle.set_math("tf32")
