@@ -272,6 +272,10 @@ def gpu_arm(args):
         d_ms, d_fl, d_n = (prof[f] for f in kernels[dom])
         o_ms, o_fl, o_n = (prof[f] for f in kernels[other])
         achieved = d_fl / (d_ms / 1e3) / 1e12 if d_ms > 0 else 0.0
+        # dram__bytes_read + dram__bytes_write per launch of the generic kernel, from one ncu pass over a
+        # forward pass of this exact workload (profiles/vgg16_b256_launch_list.md); other workloads: not captured
+        traffic = 819.0e6 if (wl_name == "vgg16" and batch == 256 and world == 1 and args.math == "tf32"
+                              and dom == "gemm_tf32_tcgen05_kernel") else None
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
             try:
@@ -295,7 +299,8 @@ def gpu_arm(args):
             "gpu_launches": launches,
             "clocks": clocks,
             "roofline": {"bound": "tensor", "achieved": round(achieved, 2), "peak": round(tf32_peak, 1), "unit": "TFLOP/s",
-                         "frac": round(achieved / tf32_peak, 4) if tf32_peak else None, "traffic": None,
+                         "frac": round(achieved / tf32_peak, 4) if tf32_peak else None, "traffic": traffic,
+                         "traffic_unit": "bytes per launch (ncu dram read+write)",
                          "kernel": dom,
                          "launches_per_step": d_n / K, "kernel_ms_per_step": round(d_ms / K, 4),
                          "other_tensor_kernel": {"kernel": other, "launches_per_step": o_n / K,
