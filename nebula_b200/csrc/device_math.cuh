@@ -55,6 +55,30 @@ __device__ __forceinline__ float apply_activation(float x, int act) {
 // instruction stream of loops that almost always run relu / leaky / linear.
 static __device__ __noinline__ float apply_activation_call(float x, int act) { return apply_activation(x, act); }
 
+// One LSTM cell update (lstm_layer.cc:286-311) from the four gate pre-activations of a hidden unit: out of line to
+// keep the GEMM epilogue small, with the four gate activations inline so that their exp chains overlap. The
+// products and the sum round to fp32 separately, as the CPU path's loops do.
+static __device__ __noinline__ float2 lstm_cell_unit(float zi, float zf, float zg, float zo, float c_prev) {
+    const float ig = apply_activation(zi, NB_ACT_LOGISTIC);
+    const float fg = apply_activation(zf, NB_ACT_LOGISTIC);
+    const float gg = apply_activation(zg, NB_ACT_TANH);
+    const float og = apply_activation(zo, NB_ACT_LOGISTIC);
+    const float c = __fadd_rn(__fmul_rn(c_prev, fg), __fmul_rn(ig, gg));
+    return make_float2(c, __fmul_rn(apply_activation(c, NB_ACT_TANH), og));
+}
+
+// The same update with the gate activations evaluated in fp32 (expf/tanhf, a few ulp from the double formulas):
+// used by the TF32 GEMM epilogue, where the pre-activations already carry ~1e-3 of operand rounding and the few
+// epilogue threads of a small-batch step cannot hide double-precision latency.
+static __device__ __noinline__ float2 lstm_cell_unit_f32(float zi, float zf, float zg, float zo, float c_prev) {
+    const float ig = 1.0f / (1.0f + expf(-zi));
+    const float fg = 1.0f / (1.0f + expf(-zf));
+    const float gg = tanhf(zg);
+    const float og = 1.0f / (1.0f + expf(-zo));
+    const float c = __fadd_rn(__fmul_rn(c_prev, fg), __fmul_rn(ig, gg));
+    return make_float2(c, __fmul_rn(tanhf(c), og));
+}
+
 // relu, leaky and linear inline; everything else through the out-of-line copy
 __device__ __forceinline__ float apply_activation_fast(float x, int act) {
     if (act == NB_ACT_RELU) return x > 0.0f ? x : 0.0f;

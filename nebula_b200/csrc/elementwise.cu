@@ -309,11 +309,11 @@ __global__ void lstm_cell_kernel(const float *z, const float *c_prev, float *c_o
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
         const size_t b = idx / H, j = idx - b * H;
-        const float *zr = z + b * 4 * (size_t)H;
-        const float ig = apply_activation(zr[j], NB_ACT_LOGISTIC);
-        const float fg = apply_activation(zr[H + j], NB_ACT_LOGISTIC);
-        const float gg = apply_activation(zr[2 * (size_t)H + j], NB_ACT_TANH);
-        const float og = apply_activation(zr[3 * (size_t)H + j], NB_ACT_LOGISTIC);
+        const float4 zr = *reinterpret_cast<const float4 *>(z + (b * (size_t)H + j) * 4);     // [unit][i,f,g,o]
+        const float ig = apply_activation(zr.x, NB_ACT_LOGISTIC);
+        const float fg = apply_activation(zr.y, NB_ACT_LOGISTIC);
+        const float gg = apply_activation(zr.z, NB_ACT_TANH);
+        const float og = apply_activation(zr.w, NB_ACT_LOGISTIC);
         const float cp = c_prev ? c_prev[idx] : 0.0f;
         const float c = __fadd_rn(__fmul_rn(cp, fg), __fmul_rn(ig, gg));
         const float hv = __fmul_rn(apply_activation(c, NB_ACT_TANH), og);

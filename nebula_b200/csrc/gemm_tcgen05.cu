@@ -154,7 +154,8 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
                 const int w0 = tw * p.bw * p.stride - p.pad;
                 const int h0 = th * p.bh * p.stride - p.pad;
                 const int n0 = tn * p.bn;
-                for (int kb = split * p.kb_per_split; kb < (split + 1) * p.kb_per_split; kb++) {
+                const int kb_end = min((split + 1) * p.kb_per_split, p.num_k_blocks);      // the last split may be shorter
+                for (int kb = split * p.kb_per_split; kb < kb_end; kb++) {
                     if (!(ok = mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status))) break;
                     const int tap = kb / p.c_blocks, cb = kb - tap * p.c_blocks;
                     const int kh = tap / p.ksize, kw = tap - kh * p.ksize;
@@ -185,7 +186,8 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
                 tc_fence_after();
                 uint32_t d_tmem = tmem_base + (uint32_t)(acc * BLOCK_N);
                 int kb_in_part = 0;
-                for (int kb = 0; kb < p.kb_per_split; kb++, kb_in_part++) {
+                const int tile_kb = min(p.kb_per_split, p.num_k_blocks - (tile % p.k_splits) * p.kb_per_split);
+                for (int kb = 0; kb < tile_kb; kb++, kb_in_part++) {
                     if (kb_in_part == p.kb_per_part) {
                         // hand this partial sum to the epilogue warps and restart in the other accumulator
                         umma_commit(&acc_full[acc]);
@@ -268,7 +270,9 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
             } else if constexpr (PROMOTE) {
                 // promoted accumulation: this group's slabs of every partial sum are added in registers
                 uint32_t sum[CH][32];
-                for (int part = 0; part < p.parts && ok; part++) {
+                const int tile_kb = min(p.kb_per_split, p.num_k_blocks - split * p.kb_per_split);
+                const int parts = (tile_kb + p.kb_per_part - 1) / p.kb_per_part;
+                for (int part = 0; part < parts && ok; part++) {
                     if (!(ok = epilogue_all(mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status), bar_id))) break;
                     tc_fence_after();
 #pragma unroll
@@ -454,7 +458,7 @@ void launch(nb_handle_s *h, const TcParams &p) {
         NB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
         configured = true;
     }
-    const int tiles = p.m_tiles * p.n_tiles;
+    const int tiles = p.m_tiles * p.n_tiles * p.k_splits;
     const int grid = std::max(1, std::min(tiles, h->sm_count));
     const int threads = (THREE || p.gather) ? 448 : 320;
     kern<<<grid, threads, C::SMEM_BYTES, h->stream>>>(p);
@@ -534,10 +538,10 @@ void gemm_tc(nb_handle_s *h, const GemmArgs &a, bool three_pass) {
     p.ksize = g.ksize; p.stride = g.stride; p.pad = g.pad;
     p.c_blocks = (kc + BLOCK_K - 1) / BLOCK_K;
     p.num_k_blocks = taps * p.c_blocks;
-    if (S > 1 && (p.num_k_blocks % S || a.y_pool || a.addend || three_pass || a.scale || a.shift || a.act != NB_ACT_LINEAR))
-        throw Error(NB_ERR_INVALID_ARG, "split-K needs a number of K blocks divisible by the splits and a plain epilogue");
+    p.kb_per_split = (p.num_k_blocks + S - 1) / S;
+    if (S > 1 && ((long)(S - 1) * p.kb_per_split >= p.num_k_blocks || a.y_pool || a.addend || three_pass || a.scale || a.shift || a.act != NB_ACT_LINEAR))
+        throw Error(NB_ERR_INVALID_ARG, "split-K needs non-empty splits of ceil(K blocks / splits) blocks and a plain epilogue");
     p.k_splits = S;
-    p.kb_per_split = p.num_k_blocks / S;
     p.m_tiles = p.tiles_w * p.tiles_h * p.tiles_n;
     p.e.N = a.N;
     p.tx_bytes_a = BLOCK_K * 4 * box.bw * box.bh * box.bn;
@@ -554,6 +558,15 @@ void gemm_tc(nb_handle_s *h, const GemmArgs &a, bool three_pass) {
         if (!a.a_is_conv || (g.OW & 1) || (g.OH & 1) || (a.N % 4) || !aligned16(a.y_pool) || a.addend)
             throw Error(NB_ERR_UNSUPPORTED, "fused 2x2 pooling needs even output extents and a 16-byte aligned NHWC tensor");
         p.e.tma_store = 0;
+    } else if (a.lstm_H > 0) {
+        if (a.a_is_conv || S > 1 || a.N != 4 * a.lstm_H || !a.lstm_c || !a.lstm_h)
+            throw Error(NB_ERR_INVALID_ARG, "LSTM epilogue needs a plain [M,4H] product and c/h outputs");
+        p.e.tma_store = 0;
+        p.e.lstm_H = a.lstm_H; p.e.lstm_c_prev = a.lstm_c_prev; p.e.lstm_c = a.lstm_c; p.e.lstm_h = a.lstm_h;
+        p.e.lstm_h_round = a.lstm_h_round;
+        p.e.lstm_f32 = three_pass ? 0 : 1;
+        p.e.lstm_vec = (a.lstm_H % 8) == 0 && aligned16(a.lstm_c) && aligned16(a.lstm_h) &&
+                       (!a.lstm_c_prev || aligned16(a.lstm_c_prev)) && (!a.lstm_h_round || aligned16(a.lstm_h_round));
     } else if (!a.y) {
         throw Error(NB_ERR_INVALID_ARG, "GEMM without an output tensor");
     }
@@ -565,7 +578,8 @@ void gemm_tc(nb_handle_s *h, const GemmArgs &a, bool three_pass) {
     const bool promote = three_pass || (long)p.kb_per_split * BLOCK_K >= 8192;   // per split when K is split
     int block_n = 256;
     if (three_pass || gather || promote) block_n = 128;
-    while (block_n > 64) {
+    if (a.block_n_hint) block_n = std::min(block_n, a.block_n_hint);
+    while (block_n > 64 && !a.block_n_hint) {
         const long tiles = (long)p.m_tiles * S * ((a.N + block_n - 1) / block_n);
         if (a.N > block_n / 2 && tiles >= h->sm_count) break;
         if (a.N > block_n / 2 && (long)p.m_tiles * ((a.N + block_n / 2 - 1) / (block_n / 2)) > 2L * h->sm_count) break;

@@ -128,9 +128,18 @@ struct GemmArgs {
     long ldy = 0;
     // tensor-core conv only: write the 2x2 stride-2 max-pooled output [B][OH/2][OW/2][N] here INSTEAD of y
     float *y_pool = nullptr;
-    // plain matrices only: contract K in `split_k` independent slices; slice s writes y + s*M*ldy
+    // tensor-core kernel, plain matrices: the N = 4*lstm_H columns are gate pre-activations laid out
+    // [hidden unit][i,f,g,o]; the epilogue runs the LSTM cell update and writes c_t, h_t (and a TF32-rounded
+    // copy of h_t) [M][lstm_H] instead of y
+    int lstm_H = 0;
+    const float *lstm_c_prev = nullptr;
+    float *lstm_c = nullptr, *lstm_h = nullptr, *lstm_h_round = nullptr;
+    // plain matrices only: contract K in `split_k` slices of ceil(K blocks / split_k) 32-wide blocks (the last may be
+    // shorter, none empty); slice s writes y + s*M*ldy
     // (y must hold split_k * M * ldy floats; the caller reduces the slices and applies the epilogue)
     int split_k = 1;
+    // tensor-core kernel: tile width in output columns (64, 128 or 256) instead of the built-in choice; 0 = automatic
+    int block_n_hint = 0;
     double algo_flops = 0;          // algorithmic FLOPs of this launch for profiling (0: 2*M*N*Kc*taps)
 };
 
@@ -171,7 +180,7 @@ void launch_fc_permute(nb_handle_s *h, const float *w, float *dst, int out, int 
 // sum of S slices [S][M][N] + folded scale/shift + activation (+ TF32 rounding) -> y [M][N]
 void launch_splitk_reduce(nb_handle_s *h, const float *ws, int S, int M, int N, const float *scale, const float *shift,
                           int act, bool round_tf32, float *y);
-// LSTM cell: z [B,4H] (gate blocks i,f,g,o) -> c_t, h_t (+ TF32-rounded copy of h_t)
+// LSTM cell: z [B,4H] laid out [hidden unit][i,f,g,o] -> c_t, h_t (+ TF32-rounded copy of h_t)
 void launch_lstm_cell(nb_handle_s *h, const float *z, const float *c_prev, float *c_out, float *h_out,
                       float *h_round, int B, int H);
 

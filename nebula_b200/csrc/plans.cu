@@ -306,21 +306,29 @@ void FcPlan::forward(const float *x, float *y, const ForwardOpts &o, int rows) {
     w.ensure_split(h);
     a.b = w.hi.p; a.b_lo = w.lo.p;
     // Few rows and a long contraction (weight streaming): split K so that every SM pulls weights.
-    int S = 1;
+    int S = 1, block_n = 0;
     if (pth == PATH_TC && !o.addend && (d.outputs % 4) == 0 && d.inputs >= 2048) {
-        const int kblocks = d.inputs / 32;
-        // chosen from K and N only, never from the batch: a batch and its slices add in the same order
-        const long tiles = (d.outputs + 127) / 128;
-        const int want = (int)std::min<long>(16, (2L * h->sm_count) / std::max<long>(1, tiles));
-        if ((d.inputs % 32) == 0)
-            for (int s = want; s >= 2; s--)
-                if (kblocks % s == 0 && kblocks / s >= 8) { S = s; break; }
+        // Chosen from K, N and the SM count only, never from the batch: a batch and its slices add in the same
+        // order.  Wide tiles keep the most weight bytes in flight per SM; the split count then fills the SMs, and
+        // of the three tile widths the one that leaves the fewest SMs idle in the last wave wins.
+        const int kblocks = (d.inputs + 31) / 32;
+        double best = 0.0;
+        for (int bn = 256; bn >= 64; bn /= 2) {
+            const int nt = (d.outputs + bn - 1) / bn;
+            int s = std::max(1, std::min({32, h->sm_count / nt, kblocks / 8}));
+            const int per = (kblocks + s - 1) / s;
+            s = (kblocks + per - 1) / per;
+            const long tiles = (long)nt * s;
+            const double fill = (double)tiles / (double)(((tiles + h->sm_count - 1) / h->sm_count) * h->sm_count);
+            if (fill > best + 0.05) { best = fill; S = s; block_n = bn; }
+        }
+        if (S == 1) block_n = 0;
     }
     if (S > 1) {
         const size_t need = (size_t)S * M * d.outputs;
         if (split_ws.n < need) split_ws.alloc(need);
         GemmArgs sa = a;
-        sa.split_k = S;
+        sa.split_k = S; sa.block_n_hint = block_n;
         sa.scale = nullptr; sa.shift = nullptr; sa.act = NB_ACT_LINEAR; sa.round_out_tf32 = false;
         sa.y = split_ws.p; sa.ldy = d.outputs;
         sa.algo_flops = 2.0 * (double)M * d.outputs * d.inputs;
@@ -376,11 +384,14 @@ void LstmPlan::set_weights(const float *stream, size_t count, int mem) {
             const size_t gin = side ? in : H;
             std::vector<float> sc, s1;
             fold_bn(H, b.bias, b.g, b.m, b.v, d.batch_normalize != 0, sc, s1);
-            float *dst = (side ? u.data() : wr.data()) + (size_t)gate * H * gin;
+            // output row of hidden unit r, gate `gate`: 4*r + gate (a thread of the GEMM epilogue then holds all
+            // four gates of a unit in neighbouring columns)
+            float *dst = side ? u.data() : wr.data();
             for (int r = 0; r < H; r++) {
                 const float s = sc.empty() ? 1.0f : sc[r];
-                for (size_t c = 0; c < gin; c++) dst[(size_t)r * gin + c] = b.w[(size_t)r * gin + c] * s;
-                sh[(size_t)gate * H + r] += s1[r];
+                const size_t row = (size_t)4 * r + gate;
+                for (size_t c = 0; c < gin; c++) dst[row * gin + c] = b.w[(size_t)r * gin + c] * s;
+                sh[row] += s1[r];
             }
         }
     }
@@ -434,23 +445,26 @@ void LstmPlan::forward(const float *x, float *out, float *cell, bool x_rounded, 
     // 2. the recurrence: z_t = pre_t + h_{t-1} * W^T, then the cell update
     for (int t = 0; t < T; t++) {
         const float *zt = pre.p + (size_t)t * B * 4 * H;
+        float *ct = cell + (size_t)t * B * H, *ht = out + (size_t)t * B * H, *hrt = hr ? hr + (size_t)t * B * H : nullptr;
         if (t > 0) {
             GemmArgs a;
             const float *hprev = (tc_w && !three) ? hr + (size_t)(t - 1) * B * H : out + (size_t)(t - 1) * B * H;
             a.a = hprev; a.lda = H; a.ldb = H; a.M = B; a.N = 4 * H; a.Kc = H;
-            a.addend = zt; a.ld_addend = 4 * H; a.act = NB_ACT_LINEAR; a.y = z.p; a.ldy = 4 * H;
+            a.addend = zt; a.ld_addend = 4 * H; a.act = NB_ACT_LINEAR;
             if (tc_w) {
+                // the cell update runs in the GEMM epilogue: one launch per time step
                 ww.ensure_split(h);
                 a.b = ww.hi.p; a.b_lo = ww.lo.p;
+                a.lstm_H = H; a.lstm_c_prev = cell + (size_t)(t - 1) * B * H; a.lstm_c = ct; a.lstm_h = ht; a.lstm_h_round = hrt;
                 gemm_tc(h, a, three);
-            } else {
-                a.b = ww.exact.p;
-                gemm_simt(h, a);
+                continue;
             }
+            a.y = z.p; a.ldy = 4 * H;
+            a.b = ww.exact.p;
+            gemm_simt(h, a);
             zt = z.p;
         }
-        launch_lstm_cell(h, zt, t ? cell + (size_t)(t - 1) * B * H : nullptr, cell + (size_t)t * B * H,
-                         out + (size_t)t * B * H, hr ? hr + (size_t)t * B * H : nullptr, B, H);
+        launch_lstm_cell(h, zt, t ? cell + (size_t)(t - 1) * B * H : nullptr, ct, ht, hrt, B, H);
     }
 }
 

@@ -35,6 +35,13 @@ struct EpiParams {
     int tma_store;              // y meets TMA's rules: slabs leave through a tensor map; else plain stores
     int pool;                   // fuse the following 2x2 stride-2 max-pool: only the pooled tensor is written
     int N;                      // valid output columns
+    // LSTM mode (lstm_H > 0): columns are gate pre-activations laid out [hidden unit][i,f,g,o]; instead of
+    // storing them the epilogue runs the cell update (lstm_layer.cc:286-311) and writes c_t, h_t [rows][H]
+    int lstm_H;
+    int lstm_vec;               // H % 8 == 0 and 16-byte aligned state tensors: 128-bit loads and stores
+    int lstm_f32;               // gate activations in fp32 (TF32 mode) instead of the double formulas
+    const float *lstm_c_prev;   // may be null (c_{t-1} = 0)
+    float *lstm_c, *lstm_h, *lstm_h_round;      // lstm_h_round may be null
 };
 // Per thread: its row of the staging slab (-1: this accumulator row is not an output pixel), the
 // output pixel index for plain stores / addend reads, and whether that pixel exists.
@@ -87,6 +94,9 @@ __device__ __forceinline__ bool mbar_try_wait_parked(uint64_t *bar, uint32_t par
         : "memory");
     return ok != 0;
 }
+#ifndef NB_PARK_NS
+#define NB_PARK_NS 20000u
+#endif
 // Bounded wait.  Returns false when the CTA is aborting (this wait or another ran out).
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -94,7 +104,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
     for (;;) {
 #pragma unroll 1
         for (int i = 0; i < 32; i++)
-            if (mbar_try_wait_parked(bar, parity, 20000u)) return true;
+            if (NB_PARK_NS ? mbar_try_wait_parked(bar, parity, NB_PARK_NS) : mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
         if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
             *abort_flag = 1;
@@ -259,6 +269,54 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams &e, const CUtenso
             for (int j = 0; j < 32; j++)
                 if (col0 + j < e.addend_cols) v[j] = __float_as_uint(__uint_as_float(v[j]) + arow[j]);
         }
+    }
+    if (e.lstm_H > 0) {
+        // 32 columns = 8 hidden units x (i, f, g, o): the cell update of this row's units, with the CPU
+        // path's separate fp32 roundings (no fused multiply-add)
+        const int j0 = col0 >> 2;
+        if (rw.row_ok && j0 < e.lstm_H) {
+            const long idx0 = rw.grow * e.lstm_H + j0;
+            float cp[8], cn[8], hn[8];
+            // all of c_{t-1} first: the eight loads overlap instead of one round trip per unit
+            if (!e.lstm_c_prev) {
+#pragma unroll
+                for (int u = 0; u < 8; u++) cp[u] = 0.0f;
+            } else if (e.lstm_vec) {
+                const float4 lo = *reinterpret_cast<const float4 *>(e.lstm_c_prev + idx0);
+                const float4 hi = *reinterpret_cast<const float4 *>(e.lstm_c_prev + idx0 + 4);
+                cp[0] = lo.x; cp[1] = lo.y; cp[2] = lo.z; cp[3] = lo.w; cp[4] = hi.x; cp[5] = hi.y; cp[6] = hi.z; cp[7] = hi.w;
+            } else {
+#pragma unroll
+                for (int u = 0; u < 8; u++) cp[u] = j0 + u < e.lstm_H ? e.lstm_c_prev[idx0 + u] : 0.0f;
+            }
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                const float zi = __uint_as_float(v[4 * u]), zf = __uint_as_float(v[4 * u + 1]);
+                const float zg = __uint_as_float(v[4 * u + 2]), zo = __uint_as_float(v[4 * u + 3]);
+                const float2 ch = e.lstm_f32 ? lstm_cell_unit_f32(zi, zf, zg, zo, cp[u]) : lstm_cell_unit(zi, zf, zg, zo, cp[u]);
+                cn[u] = ch.x; hn[u] = ch.y;
+            }
+            if (e.lstm_vec) {
+#pragma unroll
+                for (int q = 0; q < 2; q++) {
+                    *reinterpret_cast<float4 *>(e.lstm_c + idx0 + 4 * q) = make_float4(cn[4 * q], cn[4 * q + 1], cn[4 * q + 2], cn[4 * q + 3]);
+                    *reinterpret_cast<float4 *>(e.lstm_h + idx0 + 4 * q) = make_float4(hn[4 * q], hn[4 * q + 1], hn[4 * q + 2], hn[4 * q + 3]);
+                    if (e.lstm_h_round)
+                        *reinterpret_cast<float4 *>(e.lstm_h_round + idx0 + 4 * q) = make_float4(
+                            round_tf32(hn[4 * q]), round_tf32(hn[4 * q + 1]), round_tf32(hn[4 * q + 2]), round_tf32(hn[4 * q + 3]));
+                }
+            } else {
+#pragma unroll
+                for (int u = 0; u < 8; u++) {
+                    if (j0 + u < e.lstm_H) {
+                        e.lstm_c[idx0 + u] = cn[u];
+                        e.lstm_h[idx0 + u] = hn[u];
+                        if (e.lstm_h_round) e.lstm_h_round[idx0 + u] = round_tf32(hn[u]);
+                    }
+                }
+            }
+        }
+        return;
     }
     // activation: the common ones inline, the rest through one out-of-line call per value
     if (e.act == NB_ACT_RELU) {

@@ -2,6 +2,7 @@
 
     python -m nebula_b200.microbench conv --batch 64 --channels 256 --size 56 --filters 256 --k 3 --pad 1
     python -m nebula_b200.microbench fc --batch 256 --inputs 25088 --outputs 4096
+    python -m nebula_b200.microbench lstm --batch 64 --inputs 1024 --outputs 1024 --steps 128
     python -m nebula_b200.microbench sweep        # the single-convolution sweep (batch 64, stride 1)
 
 Prints one JSON line per case: device time per call (CUDA events on the stream
@@ -69,12 +70,34 @@ def bench_fc(h, batch, inputs, outputs, math, iters=10, warmup=3):
                 tflops=round(flops / ms / 1e9, 1), gbs=round(nbytes / ms / 1e6, 1))
 
 
+def bench_lstm(h, batch, inputs, hidden, steps, math, iters=10, warmup=3):
+    """One LSTM layer over `steps` time steps: the input-side GEMM plus `steps - 1` recurrent GEMMs with the cell
+    update in their epilogue."""
+    import numpy as np
+    from .workloads import NetBuilder
+    h.set_math(math)
+    b = NetBuilder("lstm", batch, input_size=inputs, time_steps=steps)
+    b.lstm(hidden, bound=1.0 / 32)
+    wl = b.build("normal")
+    plan = api.Lstm(h, steps, batch, inputs, hidden, False, "linear")
+    plan.set_weights(torch.from_numpy(np.ascontiguousarray(wl.make_weights(3))).cuda())
+    x = torch.randn(steps * batch, inputs, device="cuda")
+    out = torch.empty(steps, batch, hidden, device="cuda")
+    fwd = lambda: h.check(h.lib.nb_lstm_forward(plan.p, x.data_ptr(), out.data_ptr(), None))
+    ms = _time(fwd, iters, warmup)
+    h.synchronize()
+    flops = 2.0 * steps * batch * 4 * hidden * (inputs + hidden)
+    plan.close()
+    return dict(op="lstm", batch=batch, inputs=inputs, hidden=hidden, steps=steps, math=math, ms=round(ms, 4),
+                us_per_step=round(ms * 1e3 / steps, 2), tflops=round(flops / ms / 1e9, 1))
+
+
 SWEEP = [(256, 56, 256, 3, 1), (512, 14, 512, 3, 1), (64, 56, 256, 1, 0)]
 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["conv", "fc", "sweep", "vgg"])
+    ap.add_argument("op", choices=["conv", "fc", "lstm", "sweep", "vgg"])
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--channels", type=int, default=256)
     ap.add_argument("--size", type=int, default=56)
@@ -84,6 +107,7 @@ def main():
     ap.add_argument("--pad", type=int, default=1)
     ap.add_argument("--inputs", type=int, default=4096)
     ap.add_argument("--outputs", type=int, default=4096)
+    ap.add_argument("--steps", type=int, default=128, help="lstm: time steps")
     ap.add_argument("--math", default="tf32")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
@@ -93,6 +117,8 @@ def main():
         print(json.dumps(bench_conv(h, a.batch, a.channels, a.size, a.filters, a.k, a.stride, a.pad, a.math, a.iters, a.warmup)))
     elif a.op == "fc":
         print(json.dumps(bench_fc(h, a.batch, a.inputs, a.outputs, a.math, a.iters, a.warmup)))
+    elif a.op == "lstm":
+        print(json.dumps(bench_lstm(h, a.batch, a.inputs, a.outputs, a.steps, a.math, a.iters, a.warmup)))
     elif a.op == "sweep":
         for c, s, f, k, p in SWEEP:
             print(json.dumps(bench_conv(h, a.batch, c, s, f, k, 1, p, a.math, a.iters, a.warmup)), flush=True)
