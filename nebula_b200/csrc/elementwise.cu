@@ -4,14 +4,22 @@
 // All are grid-stride, bounds-checked, and use 128-bit accesses where the
 // innermost extent allows.
 #include <algorithm>
+#include <cstdlib>
 
 #include "device_math.cuh"
 #include "nb_internal.h"
 
 namespace nb {
 
+// NEBULA_B200_SYNC_LAUNCHES=1 in the environment waits for every kernel before returning, so that an asynchronous
+// device error is reported against the launch that caused it (debugging aid; off by default).
 void check_launch(const char *what) {
+    static const bool sync_launches = [] {
+        const char *v = std::getenv("NEBULA_B200_SYNC_LAUNCHES");
+        return v && *v && *v != '0';
+    }();
     cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess && sync_launches) e = cudaDeviceSynchronize();
     if (e != cudaSuccess) throw Error(NB_ERR_CUDA, std::string(what) + " launch: " + cudaGetErrorString(e));
 }
 

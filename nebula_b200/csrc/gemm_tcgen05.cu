@@ -23,7 +23,7 @@
 // Warp roles (320 threads; 448 with the extra operand warps):
 //   warp 0      TMA producer (one elected lane)
 //   warp 1      TMEM allocation + MMA issue (one elected lane)
-//   warps 2-5   epilogue (TMEM -> registers -> global)
+//   warps 2-9   epilogue, two groups of four (TMEM -> registers -> shared-memory slab -> TMA store)
 //   warps 10-13 three-pass mode: split each A tile into hi/lo TF32 terms; gather mode: build the
 //               A tile in shared memory from a strided tensor (3-channel input layers)
 //
@@ -141,6 +141,8 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
 
     if (warp == 0) {
         // ------------------------------------------------------ TMA producer
+        // One thread issues every copy.  Its loop is the floor under the K-block rate of narrow tiles (a few hundred
+        // cycles per issued copy), so the K-block coordinates advance by increments instead of divisions.
         if (elect_one()) {
             int stage = 0;
             uint32_t phase = 0;
@@ -154,19 +156,25 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
                 const int w0 = tw * p.bw * p.stride - p.pad;
                 const int h0 = th * p.bh * p.stride - p.pad;
                 const int n0 = tn * p.bn;
-                const int kb_end = min((split + 1) * p.kb_per_split, p.num_k_blocks);      // the last split may be shorter
-                for (int kb = split * p.kb_per_split; kb < kb_end; kb++) {
+                const int kb0 = split * p.kb_per_split;
+                const int kb_end = min(kb0 + p.kb_per_split, p.num_k_blocks);      // the last split may be shorter
+                int tap = kb0 / p.c_blocks, cb = kb0 - tap * p.c_blocks;
+                int kh = tap / p.ksize, kw = tap - kh * p.ksize;
+                const uint32_t tx_bytes = (uint32_t)((p.gather ? 0 : p.tx_bytes_a) + C::B_STAGE_BYTES * (THREE ? 2 : 1));
+                for (int kb = kb0; kb < kb_end; kb++) {
                     if (!(ok = mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status))) break;
-                    const int tap = kb / p.c_blocks, cb = kb - tap * p.c_blocks;
-                    const int kh = tap / p.ksize, kw = tap - kh * p.ksize;
                     uint8_t *sa = smem + stage * C::STAGE_BYTES;
                     uint8_t *sb = sa + A_STAGE_BYTES;
-                    mbar_expect_tx(&full[stage], (uint32_t)((p.gather ? 0 : p.tx_bytes_a) + C::B_STAGE_BYTES * (THREE ? 2 : 1)));
+                    mbar_expect_tx(&full[stage], tx_bytes);
                     if (!p.gather) tma_load_4d(sa, &p.tm_a, &full[stage], cb * BLOCK_K, w0 + kw, h0 + kh, n0);
                     tma_load_3d(sb, &p.tm_b, &full[stage], cb * BLOCK_K, n_tile * BLOCK_N, tap);
                     if (THREE)
                         tma_load_3d(sb + C::B_STAGE_BYTES + A_STAGE_BYTES, &p.tm_b_lo, &full[stage], cb * BLOCK_K,
                                     n_tile * BLOCK_N, tap);
+                    if (++cb == p.c_blocks) {
+                        cb = 0; tap++;
+                        if (++kw == p.ksize) { kw = 0; kh++; }
+                    }
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
             }
@@ -643,16 +651,27 @@ void gemm_tc(nb_handle_s *h, const GemmArgs &a, bool three_pass) {
     }
 
     ProfileScope prof(h, 0, a.algo_flops > 0 ? a.algo_flops : 2.0 * (double)a.M * a.N * a.Kc * taps);
-    if (three_pass) {
-        if (block_n == 128) launch<128, true, true>(h, p);
-        else launch<64, true, true>(h, p);
-    } else if (promote) {
-        if (block_n == 128) launch<128, false, true>(h, p);
-        else launch<64, false, true>(h, p);
-    } else {
-        if (block_n == 256) launch<256, false, false>(h, p);
-        else if (block_n == 128) launch<128, false, false>(h, p);
-        else launch<64, false, false>(h, p);
+    try {
+        if (three_pass) {
+            if (block_n == 128) launch<128, true, true>(h, p);
+            else launch<64, true, true>(h, p);
+        } else if (promote) {
+            if (block_n == 128) launch<128, false, true>(h, p);
+            else launch<64, false, true>(h, p);
+        } else {
+            if (block_n == 256) launch<256, false, false>(h, p);
+            else if (block_n == 128) launch<128, false, false>(h, p);
+            else launch<64, false, false>(h, p);
+        }
+    } catch (const Error &err) {
+        // name the launch: an asynchronous fault is otherwise hard to place
+        throw Error(err.code, std::string(err.what()) + " [M=" + std::to_string(a.M) + " N=" + std::to_string(a.N) + " K=" +
+                                  std::to_string(a.Kc) + " taps=" + std::to_string(taps) + " stride=" + std::to_string(g.stride) +
+                                  " out=" + std::to_string(g.OW) + "x" + std::to_string(g.OH) + "x" + std::to_string(g.batch) +
+                                  " box=" + std::to_string(box.bw) + "x" + std::to_string(box.bh) + "x" + std::to_string(box.bn) +
+                                  " block_n=" + std::to_string(block_n) + " splits=" + std::to_string(S) +
+                                  (gather ? " gather" : "") + (three_pass ? " 3xtf32" : "") + (pool ? " pool" : "") +
+                                  (a.addend ? " addend" : "") + (a.lstm_H ? " lstm" : "") + "]");
     }
 }
 

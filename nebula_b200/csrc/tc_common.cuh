@@ -94,9 +94,6 @@ __device__ __forceinline__ bool mbar_try_wait_parked(uint64_t *bar, uint32_t par
         : "memory");
     return ok != 0;
 }
-#ifndef NB_PARK_NS
-#define NB_PARK_NS 20000u
-#endif
 // Bounded wait.  Returns false when the CTA is aborting (this wait or another ran out).
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -104,7 +101,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
     for (;;) {
 #pragma unroll 1
         for (int i = 0; i < 32; i++)
-            if (NB_PARK_NS ? mbar_try_wait_parked(bar, parity, NB_PARK_NS) : mbar_try_wait(bar, parity)) return true;
+            if (mbar_try_wait_parked(bar, parity, 20000u)) return true;
         if (*abort_flag) return false;
         if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
             *abort_flag = 1;
