@@ -265,6 +265,41 @@ __global__ void weight_pack_kernel(const float *w, float *dst, int F, int C, int
     }
 }
 
+// ------------------------------------------------------ first-layer row windows
+// A layer with at most 4 input channels is fed to the tensor cores one filter ROW at a time: in a pixel-major
+// tensor with 4 floats per pixel, the k taps of a filter row are one contiguous run of 4*k floats, which a TMA box
+// can fetch for a whole tile of output pixels (overlapping windows, 16-byte stride).  The horizontal padding is
+// physical (zero pixels), the vertical padding is TMA's out-of-bounds fill.
+__global__ void weight_rowwin_kernel(const float *w, float *dst, int F, int C, int k, int inner, size_t total) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int j = (int)(i % inner);
+        const size_t f = (i / inner) % F;
+        const int kh = (int)(i / ((size_t)inner * F));
+        const int kw = j >> 2, c = j & 3;
+        dst[i] = (kw < k && c < C) ? w[((f * C + c) * k + kh) * k + kw] : 0.0f;
+    }
+}
+__global__ void rowwin_input_kernel(const float *x, float4 *dst, int N, int C, int H, int W, int Wp, int pad, int nhwc_in,
+                                    int round, size_t total) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int pcol = (int)(i % Wp);
+        const size_t nh = i / Wp;
+        const int hrow = (int)(nh % H);
+        const size_t n = nh / H;
+        const int iw = pcol - pad;
+        float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        if (iw >= 0 && iw < W) {
+            for (int c = 0; c < C; c++) {
+                const float t = nhwc_in ? x[((n * H + hrow) * W + iw) * C + c] : x[((n * C + c) * H + hrow) * W + iw];
+                v[c] = round ? round_tf32(t) : t;
+            }
+        }
+        dst[i] = make_float4(v[0], v[1], v[2], v[3]);
+    }
+}
+
 // ---------------------------------------------------------- weight layouts
 // OIHW [F][C][k][k] -> [tap][F][Cp], zero for c >= C
 __global__ void weight_relayout_kernel(const float *w, float *dst, int F, int C, int k, int Cp, size_t total) {
@@ -472,6 +507,20 @@ void launch_weight_pack(nb_handle_s *h, const float *w, float *dst, int F, int C
     const size_t total = (size_t)F * Kpad;
     weight_pack_kernel<<<grid_for(total, h), TPB, 0, h->stream>>>(w, dst, F, C, k, Kpad, total);
     check_launch("weight_pack_kernel");
+    count_launch(h);
+}
+void launch_weight_rowwin(nb_handle_s *h, const float *w, float *dst, int F, int C, int k, int inner) {
+    const size_t total = (size_t)k * F * inner;
+    weight_rowwin_kernel<<<grid_for(total, h), TPB, 0, h->stream>>>(w, dst, F, C, k, inner, total);
+    check_launch("weight_rowwin_kernel");
+    count_launch(h);
+}
+void launch_rowwin_input(nb_handle_s *h, const float *x, float *dst, int N, int C, int H, int W, int Wp, int pad, bool nhwc_in,
+                         bool round) {
+    const size_t total = (size_t)N * H * Wp;
+    rowwin_input_kernel<<<grid_for(total, h), TPB, 0, h->stream>>>(x, reinterpret_cast<float4 *>(dst), N, C, H, W, Wp, pad,
+                                                                  nhwc_in ? 1 : 0, round ? 1 : 0, total);
+    check_launch("rowwin_input_kernel");
     count_launch(h);
 }
 void launch_weight_relayout(nb_handle_s *h, const float *w, float *dst, int F, int C, int k, int Cp) {

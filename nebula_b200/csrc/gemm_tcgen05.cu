@@ -56,7 +56,7 @@ struct TcParams {
     int bw, bh, bn;
     int tiles_w, tiles_h, tiles_n;
     int OW, OH, NB;
-    int ksize, stride, pad;
+    int ksize_w, stride, pad_w, pad_h;      // filter columns (the tap index is kh*ksize_w + kw) and paddings
     int c_blocks;               // 32-channel slices per tap
     int num_k_blocks;           // ksize*ksize*c_blocks
     int m_tiles, n_tiles;
@@ -153,13 +153,13 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
                 const int tw = m_tile % p.tiles_w;
                 const int th = (m_tile / p.tiles_w) % p.tiles_h;
                 const int tn = m_tile / (p.tiles_w * p.tiles_h);
-                const int w0 = tw * p.bw * p.stride - p.pad;
-                const int h0 = th * p.bh * p.stride - p.pad;
+                const int w0 = tw * p.bw * p.stride - p.pad_w;
+                const int h0 = th * p.bh * p.stride - p.pad_h;
                 const int n0 = tn * p.bn;
                 const int kb0 = split * p.kb_per_split;
                 const int kb_end = min(kb0 + p.kb_per_split, p.num_k_blocks);      // the last split may be shorter
                 int tap = kb0 / p.c_blocks, cb = kb0 - tap * p.c_blocks;
-                int kh = tap / p.ksize, kw = tap - kh * p.ksize;
+                int kh = tap / p.ksize_w, kw = tap - kh * p.ksize_w;
                 const uint32_t tx_bytes = (uint32_t)((p.gather ? 0 : p.tx_bytes_a) + C::B_STAGE_BYTES * (THREE ? 2 : 1));
                 for (int kb = kb0; kb < kb_end; kb++) {
                     if (!(ok = mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status))) break;
@@ -173,7 +173,7 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
                                     n_tile * BLOCK_N, tap);
                     if (++cb == p.c_blocks) {
                         cb = 0; tap++;
-                        if (++kw == p.ksize) { kw = 0; kh++; }
+                        if (++kw == p.ksize_w) { kw = 0; kh++; }
                     }
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
@@ -535,7 +535,8 @@ void gemm_tc(nb_handle_s *h, const GemmArgs &a, bool three_pass) {
     // own slab of y ([split][batch][OH][OW][N]); the caller adds the slabs and applies the epilogue.
     const int S = (!gather && a.split_k > 1) ? a.split_k : 1;
     const int kc = a.Kc;
-    const int taps = g.ksize * g.ksize;
+    const int ksize_w = g.ksize_w > 0 ? g.ksize_w : g.ksize;
+    const int taps = g.ksize * ksize_w;
     const bool pool = a.y_pool != nullptr;
     Box box = choose_box(g.OW, g.OH, g.batch, g.stride, pool, S > 1);
     p.bw = box.bw; p.bh = box.bh; p.bn = box.bn;
@@ -543,7 +544,7 @@ void gemm_tc(nb_handle_s *h, const GemmArgs &a, bool three_pass) {
     p.tiles_h = (g.OH + box.bh - 1) / box.bh;
     p.tiles_n = (g.batch + box.bn - 1) / box.bn;
     p.OW = g.OW; p.OH = g.OH; p.NB = g.batch;
-    p.ksize = g.ksize; p.stride = g.stride; p.pad = g.pad;
+    p.ksize_w = ksize_w; p.stride = g.stride; p.pad_h = g.pad; p.pad_w = g.pad_w >= 0 ? g.pad_w : g.pad;
     p.c_blocks = (kc + BLOCK_K - 1) / BLOCK_K;
     p.num_k_blocks = taps * p.c_blocks;
     p.kb_per_split = (p.num_k_blocks + S - 1) / S;

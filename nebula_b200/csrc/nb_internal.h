@@ -94,6 +94,9 @@ struct ConvGeom {
     int batch = 1, C = 1, H = 1, W = 1;     // input extents
     int OH = 1, OW = 1;                     // output extents
     int ksize = 1, stride = 1, pad = 0;
+    // tensor-core TMA path only: a filter of ksize rows x ksize_w columns (0: square) with its own horizontal padding
+    // (-1: same as pad).  Used by the row-window route, where each filter row is one run of `C` contiguous floats.
+    int ksize_w = 0, pad_w = -1;
     // element strides of the input tensor (for the CUDA-core gather path)
     long sn = 0, sc = 1, sh = 0, sw = 0;
 };
@@ -172,6 +175,11 @@ void launch_pool(nb_handle_s *h, const nb_pool_desc_t &d, const float *x, float 
 void launch_shortcut(nb_handle_s *h, const nb_shortcut_desc_t &d, const float *prev, const float *conn, float *y,
                      bool round_tf32);
 // weights OIHW [F,C,k,k] -> [k*k][F][Cp] (Cp >= C, zero padded), optionally permuting FC columns
+// first-layer row windows: [F][C][k][k] -> [kh][F][inner], column = kw*4 + c (zero elsewhere)
+void launch_weight_rowwin(nb_handle_s *h, const float *w, float *dst, int F, int C, int k, int inner);
+// NCHW or NHWC [N][C][H][W] -> [N][H][Wp][4] with `pad` zero pixels on the left, zeros on the right and in channels >= C
+void launch_rowwin_input(nb_handle_s *h, const float *x, float *dst, int N, int C, int H, int W, int Wp, int pad, bool nhwc_in,
+                         bool round);
 void launch_weight_relayout(nb_handle_s *h, const float *w_oihw, float *dst, int F, int C, int k, int Cp);
 // weights OIHW -> [F][Kpad] with column (kh,kw,c), zero padded: the B operand of the gathered-A convolution
 void launch_weight_pack(nb_handle_s *h, const float *w_oihw, float *dst, int F, int C, int k, int Kpad);

@@ -67,6 +67,10 @@ ConvPlan::ConvPlan(nb_handle_s *hh, const nb_conv2d_desc_t &desc) : nb_plan_s(NB
     const int K = d.channels * d.size * d.size;
     Kpad = (K + 31) / 32 * 32;
     pack_ok = (Cp != d.channels || d.channels < 32) && Kpad <= 384;    // the gather table lives in the kernel parameters
+    // row windows: 4 floats per pixel, a filter row of k taps is 4k floats, rounded up to whole 32-float K blocks
+    rw_inner = (4 * d.size + 31) / 32 * 32;
+    rw_wp = std::max((OW - 1) * d.stride + rw_inner / 4, d.width + 2 * d.padding);
+    rowwin_ok = d.channels <= 4 && rw_inner <= 256 && d.stride <= 8 && h->encode_tiled && h->cc_major == 10;
 }
 
 void ConvPlan::set_weights(const float *weight, const float *bias, const float *g, const float *m, const float *v,
@@ -79,6 +83,11 @@ void ConvPlan::set_weights(const float *weight, const float *bias, const float *
     w.exact.alloc((size_t)d.size * d.size * d.filters * Cp);
     w.split_ready = false;
     launch_weight_relayout(h, raw.p, w.exact.p, d.filters, d.channels, d.size, Cp);
+    if (rowwin_ok) {
+        wr.exact.alloc((size_t)d.size * d.filters * rw_inner);
+        wr.split_ready = false;
+        launch_weight_rowwin(h, raw.p, wr.exact.p, d.filters, d.channels, d.size, rw_inner);
+    }
     if (pack_ok) {
         wp.exact.alloc((size_t)d.filters * Kpad);
         wp.split_ready = false;
@@ -130,6 +139,37 @@ void ConvPlan::forward(const float *x, float *y, const ForwardOpts &o) {
     g.batch = d.batch; g.C = d.channels; g.H = d.height; g.W = d.width; g.OH = OH; g.OW = OW;
     g.ksize = d.size; g.stride = d.stride; g.pad = d.padding;
 
+    if (pth == PATH_SIMT && rowwin_ok && h->math_mode != NB_MATH_FP32) {
+        // tensor-core route for 1-4 input channels: one TMA-fetched K slice per filter row
+        const bool three = h->math_mode == NB_MATH_TF32X3;
+        const size_t need = (size_t)d.batch * d.height * rw_wp * 4;
+        if (x_rowwin.n < need) x_rowwin.alloc(need);
+        launch_rowwin_input(h, x, x_rowwin.p, d.batch, d.channels, d.height, d.width, rw_wp, d.padding, o.x_nhwc, !three);
+        GemmArgs ra;
+        ra.a = x_rowwin.p; ra.a_is_conv = true;
+        ConvGeom &rg = ra.g;
+        rg.batch = d.batch; rg.C = rw_inner; rg.H = d.height; rg.W = rw_wp - rw_inner / 4 + 1; rg.OH = OH; rg.OW = OW;
+        rg.ksize = d.size; rg.ksize_w = 1; rg.stride = d.stride; rg.pad = d.padding; rg.pad_w = 0;
+        rg.sc = 1; rg.sw = 4; rg.sh = (long)rw_wp * 4; rg.sn = (long)d.height * rw_wp * 4;
+        ra.ldb = rw_inner; ra.M = d.batch * OH * OW; ra.N = d.filters; ra.Kc = rw_inner;
+        ra.scale = has_scale ? scale.p : nullptr; ra.shift = shift.p; ra.act = d.activation;
+        ra.round_out_tf32 = o.round_out; ra.addend = o.addend; ra.ld_addend = d.filters;
+        float *yo = y;
+        if (!o.y_nhwc) {
+            NB_REQUIRE(o.addend == nullptr, "conv: addend needs NHWC output");
+            if (y_scratch.n < yout) y_scratch.alloc(yout);
+            yo = y_scratch.p;
+        }
+        ra.y = yo; ra.ldy = d.filters;
+        ra.algo_flops = 2.0 * (double)ra.M * d.filters * d.channels * d.size * d.size;
+        wr.ensure_split(h);
+        ra.b = wr.hi.p; ra.b_lo = wr.lo.p;
+        if (gemm_tc_supported(h, ra)) {
+            gemm_tc(h, ra, three);
+            if (!o.y_nhwc) launch_layout(h, yo, y, d.batch, d.filters, OH, OW, false, false);
+            return;
+        }
+    }
     if (pth == PATH_SIMT && pack_ok && h->math_mode != NB_MATH_FP32 && h->encode_tiled) {
         // tensor-core route for small channel counts: the kernel gathers the patches itself
         const bool three = h->math_mode == NB_MATH_TF32X3;

@@ -62,6 +62,12 @@ struct ConvPlan : nb_plan_s {
     bool pack_ok = false;
     int Kpad = 0;
     WeightSet wp;                   // [F][Kpad], column = (kh,kw,c)
+    // At most 4 input channels on the tensor-core path: the input is re-laid as [N][H][Wp][4] (zero pixels left and
+    // right) and every filter ROW becomes one K slice of `rw_inner` floats that TMA fetches as overlapping windows.
+    bool rowwin_ok = false;
+    int rw_inner = 0, rw_wp = 0;
+    WeightSet wr;                   // [kh][F][rw_inner], column = kw*4 + c
+    DeviceBuffer x_rowwin;
     DeviceBuffer scale, shift;
     bool has_scale = false, ready = false;
     DeviceBuffer x_scratch, y_scratch;
