@@ -60,6 +60,9 @@ struct TcParams {
     int c_blocks;               // 32-channel slices per tap
     int num_k_blocks;           // ksize*ksize*c_blocks
     int m_tiles, n_tiles;
+    // tile order: consecutive tiles share the A tile (n fastest) or, when the weights are what streams from HBM
+    // (connected layers wider than L2), the B tile (m fastest), so that the second reader finds it in L2
+    int m_fastest;
     int tx_bytes_a;             // bytes one A box load delivers
     // split-K: a tile is (m_tile, n_tile, split); split s runs K blocks [s*kb_per_split, (s+1)*kb_per_split)
     // and stores into slab s of y (batch coordinate n + s*NB): y then holds k_splits partial tensors
@@ -149,7 +152,8 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
                 const int split = tile % p.k_splits, mn = tile / p.k_splits;
-                const int m_tile = mn / p.n_tiles, n_tile = mn % p.n_tiles;
+                const int m_tile = p.m_fastest ? mn % p.m_tiles : mn / p.n_tiles;
+                const int n_tile = p.m_fastest ? mn / p.m_tiles : mn % p.n_tiles;
                 const int tw = m_tile % p.tiles_w;
                 const int th = (m_tile / p.tiles_w) % p.tiles_h;
                 const int tn = m_tile / (p.tiles_w * p.tiles_h);
@@ -251,7 +255,8 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
         bool ok = true;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
             const int split = tile % p.k_splits, mn = tile / p.k_splits;
-            const int m_tile = mn / p.n_tiles, n_tile = mn % p.n_tiles;
+            const int m_tile = p.m_fastest ? mn % p.m_tiles : mn / p.n_tiles;
+            const int n_tile = p.m_fastest ? mn / p.m_tiles : mn % p.n_tiles;
             const int tw = m_tile % p.tiles_w;
             const int th = (m_tile / p.tiles_w) % p.tiles_h;
             const int tn = m_tile / (p.tiles_w * p.tiles_h);
@@ -595,6 +600,7 @@ void gemm_tc(nb_handle_s *h, const GemmArgs &a, bool three_pass) {
         block_n /= 2;
     }
     p.n_tiles = (a.N + block_n - 1) / block_n;
+    p.m_fastest = (!a.a_is_conv && !gather && (size_t)a.N * a.Kc * 4 > ((size_t)48 << 20)) ? 1 : 0;
     // accumulation chains of at most 512 (TF32) / 128 (3xTF32) K elements in the tensor core
     p.kb_per_part = !promote ? p.kb_per_split : (three_pass ? 4 : 16);
     p.parts = (p.kb_per_split + p.kb_per_part - 1) / p.kb_per_part;

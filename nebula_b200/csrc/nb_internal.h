@@ -74,7 +74,9 @@ struct DeviceBuffer {
     ~DeviceBuffer() { release(); }
     void alloc(size_t count) {
         release();
-        if (count) NB_CHECK_CUDA(cudaMalloc((void **)&p, count * sizeof(float)));
+        // 256 bytes of tail slack: a TMA box whose rows do not start on 128-byte lines may touch the line after the
+        // tensor's last element
+        if (count) NB_CHECK_CUDA(cudaMalloc((void **)&p, count * sizeof(float) + 256));
         n = count;
     }
     void release() {

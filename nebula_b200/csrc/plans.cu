@@ -142,11 +142,16 @@ void ConvPlan::forward(const float *x, float *y, const ForwardOpts &o) {
     if (pth == PATH_SIMT && rowwin_ok && h->math_mode != NB_MATH_FP32) {
         // tensor-core route for 1-4 input channels: one TMA-fetched K slice per filter row
         const bool three = h->math_mode == NB_MATH_TF32X3;
-        const size_t need = (size_t)d.batch * d.height * rw_wp * 4;
+        // Slack before and after the tensor: the windows are 128 bytes long but start on 16-byte boundaries, the last
+        // one ends exactly at the tensor's end, and the copy engine was seen to touch memory past it (intermittent
+        // illegal-address faults when the buffer happened to end a mapping, none with 256 bytes of slack).
+        const size_t slack = (size_t)rw_wp * 4 + 64;            // one padded image row + 256 bytes, in floats
+        const size_t need = (size_t)d.batch * d.height * rw_wp * 4 + 2 * slack;
         if (x_rowwin.n < need) x_rowwin.alloc(need);
-        launch_rowwin_input(h, x, x_rowwin.p, d.batch, d.channels, d.height, d.width, rw_wp, d.padding, o.x_nhwc, !three);
+        float *xw = x_rowwin.p + slack;
+        launch_rowwin_input(h, x, xw, d.batch, d.channels, d.height, d.width, rw_wp, d.padding, o.x_nhwc, !three);
         GemmArgs ra;
-        ra.a = x_rowwin.p; ra.a_is_conv = true;
+        ra.a = xw; ra.a_is_conv = true;
         ConvGeom &rg = ra.g;
         rg.batch = d.batch; rg.C = rw_inner; rg.H = d.height; rg.W = rw_wp - rw_inner / 4 + 1; rg.OH = OH; rg.OW = OW;
         rg.ksize = d.size; rg.ksize_w = 1; rg.stride = d.stride; rg.pad = d.padding; rg.pad_w = 0;
