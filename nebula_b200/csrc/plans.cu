@@ -3,6 +3,7 @@
 #include "plans.h"
 
 #include <algorithm>
+#include <cstdlib>
 #include <cmath>
 #include <cstring>
 
@@ -70,7 +71,10 @@ ConvPlan::ConvPlan(nb_handle_s *hh, const nb_conv2d_desc_t &desc) : nb_plan_s(NB
     // row windows: 4 floats per pixel, a filter row of k taps is 4k floats, rounded up to whole 32-float K blocks
     rw_inner = (4 * d.size + 31) / 32 * 32;
     rw_wp = std::max((OW - 1) * d.stride + rw_inner / 4, d.width + 2 * d.padding);
-    rowwin_ok = d.channels <= 4 && rw_inner <= 256 && d.stride <= 8 && h->encode_tiled && h->cc_major == 10;
+    // NEBULA_B200_ROW_WINDOWS=0 (read when the plan is created) sends these layers through the in-kernel gather instead
+    const char *rw_env = std::getenv("NEBULA_B200_ROW_WINDOWS");
+    rowwin_ok = !(rw_env && *rw_env == '0') && d.channels <= 4 && rw_inner <= 256 && d.stride <= 8 && h->encode_tiled &&
+                h->cc_major == 10;
 }
 
 void ConvPlan::set_weights(const float *weight, const float *bias, const float *g, const float *m, const float *v,

@@ -268,3 +268,33 @@ def test_error_reporting(handle):
     with pytest.raises(api.NebulaError) as e:
         api.Network(handle, "[net]\nbatch=1\nheight=4\nwidth=4\nchannels=1\n[bogus]\nx=1\n")
     assert e.value.code == 5
+
+
+ROWWIN_CASES = [(2, 3, 20, 24, 32, 3, 1, 1, False, "relu"), (2, 3, 33, 31, 64, 7, 2, 3, True, "relu"),
+                (1, 3, 51, 51, 24, 11, 4, 0, False, "relu"), (3, 1, 16, 18, 16, 5, 1, 2, False, "leaky"),
+                (2, 4, 12, 12, 40, 3, 2, 1, False, "linear")]
+
+
+@pytest.mark.parametrize("mode", ["tf32", "tf32x3"])
+@pytest.mark.parametrize("case", ROWWIN_CASES, ids=lambda c: "x".join(map(str, c)))
+@pytest.mark.parametrize("route", ["1", "0"])
+def test_conv2d_row_window_and_gather_routes(handle, mode, case, route, monkeypatch):
+    """Layers with at most 4 input channels through the row-window route (default) and through the in-kernel gather
+    (NEBULA_B200_ROW_WINDOWS=0, read when the plan is created): same tolerance."""
+    from nebula_b200 import api
+    from oracle import oracle as O
+    monkeypatch.setenv("NEBULA_B200_ROW_WINDOWS", route)
+    B, C, H, W, F, k, s, p, bn, act = case
+    rng = np.random.default_rng(zlib.crc32(repr(case).encode()) + 1)
+    x = rng.standard_normal((B, C, H, W), dtype=np.float32)
+    w = (rng.standard_normal((F, C, k, k)) * np.sqrt(2.0 / (C * k * k))).astype(np.float32)
+    bias = (0.1 * rng.standard_normal(F)).astype(np.float32)
+    bnp = _bn(rng, F) if bn else None
+    ref = O.conv_forward(x, w, bias, k, s, p, act, bnp)
+    handle.set_math(mode)
+    plan = api.Conv2d(handle, B, C, H, W, F, k, s, p, bn, act, api.LAYOUT_NCHW)
+    plan.set_weights(w, bias, bnp)
+    y = plan.forward(_t(x)).cpu().numpy()
+    handle.synchronize()
+    plan.close()
+    assert_close(y, ref, mode, f"row-window conv {case}")
