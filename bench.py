@@ -274,7 +274,7 @@ def gpu_arm(args):
         achieved = d_fl / (d_ms / 1e3) / 1e12 if d_ms > 0 else 0.0
         # dram__bytes_read + dram__bytes_write per launch of the generic kernel, from one ncu pass over a
         # forward pass of this exact workload (profiles/vgg16_b256_launch_list.md); other workloads: not captured
-        traffic = 819.0e6 if (wl_name == "vgg16" and batch == 256 and world == 1 and args.math == "tf32"
+        traffic = 815.2e6 if (wl_name == "vgg16" and batch == 256 and world == 1 and args.math == "tf32"
                               and dom == "gemm_tf32_tcgen05_kernel") else None
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
