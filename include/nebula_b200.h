@@ -109,8 +109,29 @@ int nb_conv2d_set_weights(nb_plan_t plan, const float *weight, const float *bias
  * y = act(BN(W * x) + bias) with the CPU path's batch-norm formula
  * (common/batchnorm.cc:58-97).  x, y are device pointers. */
 int nb_conv2d_forward(nb_plan_t plan, const float *x, float *y);
+/* The same forward with the layers that follow it folded into its epilogue (NB_LAYOUT_NHWC plans on the
+ * tensor-core paths only; anything else returns NB_ERR_UNSUPPORTED):
+ *   residual != NULL: the [shortcut] layer that follows (shortcut_layer.cu:27-52, sampling rule of
+ *     common/utils.cc:28-60 with sample == 1): y = res_activation(conv(x) + residual), residual being the NHWC tensor
+ *     [B, res_height, res_width, res_channels] of the connected layer; the plan's own activation must be linear;
+ *   pool_out != NULL: the 2x2 stride-2 [maxpool] that follows (pooling_layer.cu:150-175): only the pooled NHWC
+ *     tensor [B, OH/2, OW/2, F] is written, y is ignored and may be NULL.
+ * One of the two at most. */
+typedef struct {
+    const float *residual;
+    int res_channels, res_height, res_width, res_activation;
+    float *pool_out;
+} nb_conv2d_fusion_t;
+int nb_conv2d_forward_fused(nb_plan_t plan, const float *x, float *y, const nb_conv2d_fusion_t *fusion);
 /* Output extents {C,H,W} of any plan. */
 int nb_plan_output_dims(nb_plan_t plan, int dims[3]);
+/* Scratch memory (the reference's per-layer `workspace`, convolutional_layer.cc:152-153,187): a plan's forward
+ * needs device scratch for layout changes, TF32-rounded operand copies and split-K partial sums.
+ * nb_plan_prepare allocates it now, for the handle's current math mode, so that the forward calls that follow
+ * allocate nothing; nb_workspace_size returns the bytes of scratch the plan holds (after prepare or a forward:
+ * what this plan needs). */
+int nb_plan_prepare(nb_plan_t plan);
+size_t nb_workspace_size(nb_plan_t plan);
 int nb_plan_destroy(nb_plan_t plan);
 
 /* --------------------------------------------------------- connected layer */
@@ -135,8 +156,9 @@ int nb_fc_forward(nb_plan_t plan, const float *x, float *y);
  * y[batch,outputs] = act(x[batch,inputs] * weight[outputs,inputs]^T + bias); all
  * pointers are device pointers, no batch-norm.  Working copies (TF32-rounded
  * operands, or the 3xTF32 weight split) live in a 16 MiB array built into the
- * library: batch*inputs + outputs*inputs + outputs floats (2*outputs*inputs + outputs
- * for 3xTF32) must fit in 4 Mi floats, else NB_ERR_INVALID_ARG.  The first call on a device looks
+ * library: batch*inputs + outputs*inputs + outputs floats (batch*inputs + 2*outputs*inputs
+ * + outputs for 3xTF32) plus 256*inputs + 32 floats of headroom behind the weights must fit
+ * in 4 Mi floats, else NB_ERR_INVALID_ARG.  The first call on a device looks
  * the array's device address up and should be made before any stream capture
  * begins.  All calls share the array: calls that overlap on the GPU race. */
 int nb_fc_forward_static(nb_handle_t handle, const float *x, const float *weight, const float *bias, int batch,
@@ -173,12 +195,25 @@ int nb_shortcut_forward(nb_handle_t handle, const nb_shortcut_desc_t *desc, cons
  * each {bias[H], weight[H*in_g], (scale,mean,var)[H] iff batch_normalize}. */
 typedef struct {
     int time_steps, batch, inputs, hidden;
-    int batch_normalize, activation;        /* section activation of the gate layers (linear) */
+    int batch_normalize, activation;        /* section activation of the eight gate layers (shipped cfgs: linear) */
 } nb_lstm_desc_t;
 int nb_lstm_plan_create(nb_handle_t handle, const nb_lstm_desc_t *desc, nb_plan_t *plan);
 int nb_lstm_set_weights(nb_plan_t plan, const float *blob_stream, size_t count, int mem);
 /* cell may be NULL; otherwise it receives c_t for every step, [T,B,H]. */
 int nb_lstm_forward(nb_plan_t plan, const float *x, float *out, float *cell);
+
+/* ---------------------------------------------------------------------- RNN */
+/* rnn_layer_t::init / init_weight / forward (rnn_layer.cc:34-141): input, hidden and output gate are three
+ * connected layers built from one section.  Per step: a_t = in(x_t); h_t = hid(t ? s_{t-1} : a_0);
+ * s_t = a_t + h_t; out_t = outg(t ? s_t : h_0).  x [T,B,in], out [T,B,H] time-major.  weights: the three
+ * connected blobs in weight-file order input, hidden, output gate. */
+typedef struct {
+    int time_steps, batch, inputs, hidden;
+    int batch_normalize, activation;
+} nb_rnn_desc_t;
+int nb_rnn_plan_create(nb_handle_t handle, const nb_rnn_desc_t *desc, nb_plan_t *plan);
+int nb_rnn_set_weights(nb_plan_t plan, const float *blob_stream, size_t count, int mem);
+int nb_rnn_forward(nb_plan_t plan, const float *x, float *out);
 
 /* ------------------------------------------------------- operator library */
 /* _<name>_activation_(out, n) (common/activations.h:38-50), in place. */
@@ -202,8 +237,9 @@ int nb_layout_convert(nb_handle_t handle, const float *src, float *dst, int batc
 
 /* ------------------------------------------------------------------ network */
 /* network_t::init / forward (models/networks/network.cc:57-63,82-122) for the
- * cfg files the reference's convolutional_t and recurrent_t accept
- * (convolutional.cc:52-122, recurrent.cc:116-176).  cfg_text is the content of a
+ * cfg files the reference's convolutional_t, recurrent_t and fully_connected_t accept
+ * (convolutional.cc:52-122, recurrent.cc:116-176, fully_connected.cc:52-120; an [rbm] section runs
+ * rbm_layer_t::forward, rbm_layer.cc:345-374).  cfg_text is the content of a
  * network.cfg; batch_override > 0 replaces [net] batch (the per-GPU shard).
  * `cost` sections are parsed and skipped at inference. */
 int nb_network_create(nb_handle_t handle, const char *cfg_text, int batch_override, nb_network_t *net);
@@ -218,6 +254,28 @@ int nb_network_forward(nb_network_t net, const float *input);
 /* Same pass from a host batch: copies it in, runs, and copies the network
  * output (see nb_network_output) back; the call returns with `output` filled. */
 int nb_network_forward_host(nb_network_t net, const float *input_host, float *output_host);
+
+/* The hand-off the reference does in load_data (models/networks/convolutional.cc:263-423) and print_results:
+ * a batch of decoded images goes to the device and the probabilities come back.  Pipelined: submit returns once the
+ * work is queued; the copy of batch i+1 (on a copy stream of the network's own, into the second of two device input
+ * buffers) overlaps the forward pass of batch i.  At most two submissions may be outstanding: the third waits for
+ * the first.  input_host and output_host must stay valid (and should be page-locked) until nb_network_wait returns.
+ *   nb_network_submit_host: an fp32 batch as nb_network_forward takes it.
+ *   nb_network_submit_u8:   decoded 8-bit images [B,H,W,C] with C = 3 (BGR, as OpenCV holds them) or 1; the
+ *     device does the reference's conversion: value/255.0 in double stored as float, planes swapped to RGB
+ *     (convolutional.cc:386-398), straight into the first layer's input layout.
+ * nb_network_wait blocks until every submitted batch is done and its output is in host memory. */
+int nb_network_submit_host(nb_network_t net, const float *input_host, float *output_host);
+int nb_network_submit_u8(nb_network_t net, const unsigned char *images_host, float *output_host);
+int nb_network_wait(nb_network_t net);
+/* One pass over decoded 8-bit images that are already on the device (same conversion). */
+int nb_network_forward_u8(nb_network_t net, const unsigned char *images_dev);
+/* Replays a forward pass as one CUDA graph once it has run with the same input pointer before (default off;
+ * no reference counterpart: the reference launches every kernel from the host).  Profiling windows
+ * (nb_profile_begin) always run the kernels one by one. */
+int nb_network_set_graph(nb_network_t net, int enable);
+/* Bytes of device memory the network holds besides weights and layer outputs (scratch of all its layers). */
+size_t nb_network_workspace_size(nb_network_t net);
 
 /* Layer fusion (default on): a 2x2 stride-2 max-pool that follows a convolution is
  * computed in that convolution's epilogue, so the convolution's own output_data is

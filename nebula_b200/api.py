@@ -53,6 +53,15 @@ class LstmDesc(C.Structure):
     _fields_ = [(n, C.c_int) for n in ("time_steps", "batch", "inputs", "hidden", "batch_normalize", "activation")]
 
 
+class RnnDesc(C.Structure):
+    _fields_ = [(n, C.c_int) for n in ("time_steps", "batch", "inputs", "hidden", "batch_normalize", "activation")]
+
+
+class ConvFusion(C.Structure):
+    _fields_ = [("residual", C.c_void_p), ("res_channels", C.c_int), ("res_height", C.c_int), ("res_width", C.c_int),
+                ("res_activation", C.c_int), ("pool_out", C.c_void_p)]
+
+
 class Profile(C.Structure):
     _fields_ = [("tc_ms", C.c_double), ("tc_flops", C.c_double), ("tc_launches", C.c_ulonglong),
                 ("simt_ms", C.c_double), ("simt_flops", C.c_double), ("simt_launches", C.c_ulonglong),
@@ -88,7 +97,10 @@ SIGNATURES = {
     "nb_conv2d_plan_create": (C.c_int, [_VP, C.POINTER(ConvDesc), C.POINTER(_VP)]),
     "nb_conv2d_set_weights": (C.c_int, [_VP, _VP, _VP, _VP, _VP, _VP, C.c_int]),
     "nb_conv2d_forward": (C.c_int, [_VP, _VP, _VP]),
+    "nb_conv2d_forward_fused": (C.c_int, [_VP, _VP, _VP, C.POINTER(ConvFusion)]),
     "nb_plan_output_dims": (C.c_int, [_VP, C.POINTER(C.c_int * 3)]),
+    "nb_plan_prepare": (C.c_int, [_VP]),
+    "nb_workspace_size": (C.c_size_t, [_VP]),
     "nb_plan_destroy": (C.c_int, [_VP]),
     "nb_fc_plan_create": (C.c_int, [_VP, C.POINTER(FcDesc), C.POINTER(_VP)]),
     "nb_fc_set_weights": (C.c_int, [_VP, _VP, _VP, _VP, _VP, _VP, C.c_int]),
@@ -99,6 +111,9 @@ SIGNATURES = {
     "nb_lstm_plan_create": (C.c_int, [_VP, C.POINTER(LstmDesc), C.POINTER(_VP)]),
     "nb_lstm_set_weights": (C.c_int, [_VP, _VP, C.c_size_t, C.c_int]),
     "nb_lstm_forward": (C.c_int, [_VP, _VP, _VP, _VP]),
+    "nb_rnn_plan_create": (C.c_int, [_VP, C.POINTER(RnnDesc), C.POINTER(_VP)]),
+    "nb_rnn_set_weights": (C.c_int, [_VP, _VP, C.c_size_t, C.c_int]),
+    "nb_rnn_forward": (C.c_int, [_VP, _VP, _VP]),
     "nb_activation_forward": (C.c_int, [_VP, C.c_int, _VP, C.c_size_t]),
     "nb_forward_bias": (C.c_int, [_VP, _VP, _VP, C.c_uint, C.c_uint, C.c_uint]),
     "nb_batchnorm_normalize": (C.c_int, [_VP, _VP, _VP, _VP, C.c_uint, C.c_uint, C.c_uint]),
@@ -113,6 +128,12 @@ SIGNATURES = {
     "nb_network_weight_count": (C.c_size_t, [_VP]),
     "nb_network_forward": (C.c_int, [_VP, _VP]),
     "nb_network_forward_host": (C.c_int, [_VP, _VP, _VP]),
+    "nb_network_submit_host": (C.c_int, [_VP, _VP, _VP]),
+    "nb_network_submit_u8": (C.c_int, [_VP, _VP, _VP]),
+    "nb_network_wait": (C.c_int, [_VP]),
+    "nb_network_forward_u8": (C.c_int, [_VP, _VP]),
+    "nb_network_set_graph": (C.c_int, [_VP, C.c_int]),
+    "nb_network_workspace_size": (C.c_size_t, [_VP]),
     "nb_network_set_fusion": (C.c_int, [_VP, C.c_int]),
     "nb_network_num_layers": (C.c_int, [_VP]),
     "nb_network_layer_info": (C.c_int, [_VP, C.c_int, C.POINTER(LayerInfo)]),
@@ -146,14 +167,14 @@ def load_library(path: Path | None = None):
     return lib
 
 
-def _ptr(t):
+def _ptr(t, dtype="float32"):
     """Device (torch) or host (numpy) buffer -> raw address."""
     if t is None:
         return None
     if isinstance(t, np.ndarray):
-        assert t.dtype == np.float32 and t.flags["C_CONTIGUOUS"]
+        assert t.dtype == np.dtype(dtype) and t.flags["C_CONTIGUOUS"]
         return t.ctypes.data
-    assert t.dtype.__str__() == "torch.float32" and t.is_contiguous(), "expected a contiguous fp32 tensor"
+    assert t.dtype.__str__() == "torch." + dtype and t.is_contiguous(), f"expected a contiguous {dtype} tensor"
     return t.data_ptr()
 
 
@@ -252,13 +273,14 @@ class Handle:
         self.check(self.lib.nb_batchnorm_scale_down(self.h, _ptr(out), _ptr(scale), channel, size, batch))
         return out
 
-    def fc_forward_static(self, x, weight, bias, activation="linear"):
+    def fc_forward_static(self, x, weight, bias, activation="linear", out=None):
         """Connected-layer forward through the entry point that allocates nothing
-        (its scratch is a fixed array inside the library); device tensors only."""
+        (its scratch is a fixed array inside the library); device tensors only.
+        Pass `out` to keep this wrapper from allocating the result tensor."""
         import torch
         batch, inputs = x.shape
         outputs = weight.shape[0]
-        y = torch.empty((batch, outputs), device=x.device, dtype=torch.float32)
+        y = out if out is not None else torch.empty((batch, outputs), device=x.device, dtype=torch.float32)
         self.check(self.lib.nb_fc_forward_static(self.h, _ptr(x), _ptr(weight), _ptr(bias), batch, inputs, outputs,
                                                  ACT[activation], _ptr(y)))
         return y
@@ -293,6 +315,14 @@ class _Plan:
         self.handle.check(self.handle.lib.nb_plan_output_dims(self.p, C.byref(d)))
         return tuple(d)
 
+    def prepare(self):
+        """Allocates the plan's scratch now (for the handle's math mode), so that forward calls allocate nothing."""
+        self.handle.check(self.handle.lib.nb_plan_prepare(self.p))
+        return self.workspace_size()
+
+    def workspace_size(self) -> int:
+        return self.handle.lib.nb_workspace_size(self.p)
+
     def close(self):
         if self.p:
             self.handle.lib.nb_plan_destroy(self.p)
@@ -321,6 +351,24 @@ class Conv2d(_Plan):
         shape = (B, Cc, OH, OW) if self.desc.layout == LAYOUT_NCHW else (B, OH, OW, Cc)
         y = torch.empty(shape, device=x.device, dtype=torch.float32)
         self.handle.check(self.handle.lib.nb_conv2d_forward(self.p, _ptr(x), _ptr(y)))
+        return y
+
+
+    def forward_fused(self, x, residual=None, res_act="linear", pool=False):
+        """NHWC plans: the following [shortcut] (residual: NHWC tensor of the connected layer) or 2x2/2 [maxpool]
+        folded into this convolution's epilogue."""
+        import torch
+        Cc, OH, OW = self.output_dims()
+        B = self.desc.batch
+        f = ConvFusion()
+        if residual is not None:
+            _, rh, rw, rc = residual.shape
+            f.residual, f.res_channels, f.res_height, f.res_width = _ptr(residual), rc, rh, rw
+            f.res_activation = ACT[res_act]
+        y = torch.empty((B, OH // 2, OW // 2, Cc) if pool else (B, OH, OW, Cc), device=x.device, dtype=torch.float32)
+        if pool:
+            f.pool_out = _ptr(y)
+        self.handle.check(self.handle.lib.nb_conv2d_forward_fused(self.p, _ptr(x), None if pool else _ptr(y), C.byref(f)))
         return y
 
 
@@ -360,6 +408,26 @@ class Lstm(_Plan):
         cell = torch.empty_like(out) if want_cell else None
         self.handle.check(self.handle.lib.nb_lstm_forward(self.p, _ptr(x), _ptr(out), _ptr(cell)))
         return (out, cell) if want_cell else out
+
+
+class Rnn(_Plan):
+    """rnn_layer_t: input, hidden and output gate as three connected layers of one section."""
+
+    def __init__(self, handle, time_steps, batch, inputs, hidden, batch_normalize=False, activation="tanh"):
+        super().__init__(handle)
+        self.desc = RnnDesc(time_steps, batch, inputs, hidden, int(batch_normalize), ACT[activation])
+        handle.check(handle.lib.nb_rnn_plan_create(handle.h, C.byref(self.desc), C.byref(self.p)))
+
+    def set_weights(self, stream):
+        self.handle.check(self.handle.lib.nb_rnn_set_weights(self.p, _ptr(stream), stream.size if isinstance(
+            stream, np.ndarray) else stream.numel(), _mem(stream)))
+
+    def forward(self, x):
+        import torch
+        d = self.desc
+        out = torch.empty((d.time_steps, d.batch, d.hidden), device=x.device, dtype=torch.float32)
+        self.handle.check(self.handle.lib.nb_rnn_forward(self.p, _ptr(x), _ptr(out)))
+        return out
 
 
 class Network:
@@ -402,6 +470,30 @@ class Network:
     def forward_host(self, x_host, out_host):
         """x_host/out_host: host buffers (numpy or pinned torch tensors); copies in, runs, copies out."""
         self.handle.check(self.handle.lib.nb_network_forward_host(self.n, _ptr(x_host), _ptr(out_host)))
+
+    def submit_host(self, x_host, out_host):
+        """Queues copy-in, forward and copy-out of one fp32 host batch and returns; at most two may be outstanding."""
+        self.handle.check(self.handle.lib.nb_network_submit_host(self.n, _ptr(x_host), _ptr(out_host)))
+
+    def submit_u8(self, images_host, out_host):
+        """Same for decoded 8-bit images [B,H,W,C] (BGR for C = 3)."""
+        assert images_host.numel() if hasattr(images_host, "numel") else images_host.size == self.input_size
+        self.handle.check(self.handle.lib.nb_network_submit_u8(self.n, _ptr(images_host, "uint8"), _ptr(out_host)))
+
+    def wait(self):
+        self.handle.check(self.handle.lib.nb_network_wait(self.n))
+
+    def forward_u8(self, images_dev):
+        """One pass over decoded 8-bit images [B,H,W,C] that are on the device."""
+        assert images_dev.numel() == self.input_size
+        self.handle.check(self.handle.lib.nb_network_forward_u8(self.n, _ptr(images_dev, "uint8")))
+
+    def set_graph(self, enable: bool):
+        """Replay passes as CUDA graphs (from the second pass with the same input buffer on)."""
+        self.handle.check(self.handle.lib.nb_network_set_graph(self.n, int(enable)))
+
+    def workspace_size(self) -> int:
+        return self.handle.lib.nb_network_workspace_size(self.n)
 
     def _fetch(self, fn, size, device):
         import torch

@@ -11,9 +11,17 @@ using namespace nb;
 
 namespace {
 
+// While a call runs, its handle's arena is the one device buffers are allocated from.
+struct ArenaScope {
+    std::shared_ptr<Arena> prev;
+    explicit ArenaScope(nb_handle_s *h) : prev(Arena::current()) { if (h) Arena::current() = h->arena; }
+    ~ArenaScope() { Arena::current() = prev; }
+};
+
 template <class F>
 int guarded(nb_handle_s *h, F &&f) {
     try {
+        ArenaScope scope(h);
         f();
         return NB_OK;
     } catch (const Error &e) {
@@ -53,8 +61,9 @@ int nb_create(int device_id, nb_handle_t *handle) {
         int count = 0;
         NB_CHECK_CUDA(cudaGetDeviceCount(&count));
         NB_REQUIRE(device_id >= 0 && device_id < count, "device id out of range");
-        NB_CHECK_CUDA(cudaSetDevice(device_id));
+        DeviceGuard g(device_id);       // the caller's current device is put back on return
         h->device = device_id;
+        h->arena = std::make_shared<Arena>();
         cudaDeviceProp prop;
         NB_CHECK_CUDA(cudaGetDeviceProperties(&prop, device_id));
         h->sm_count = prop.multiProcessorCount;
@@ -69,6 +78,15 @@ int nb_create(int device_id, nb_handle_t *handle) {
         NB_CHECK_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
         if (qres != cudaDriverEntryPointSuccess || !fn) throw Error(NB_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
         h->encode_tiled = (nb_encode_tiled_fn)fn;
+        fn = nullptr;
+        if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &fn, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            h->get_address_range = (nb_get_address_range_fn)fn;     // optional: without it operand extents go unchecked
+        // Shared-memory limits of the tensor-core kernels are a per-device setting; setting them here, with this
+        // handle's device current, also loads every kernel's code before the first forward pass.
+        gemm_tc_prepare_device();
+        conv_halo_prepare_device();
+        elementwise_prepare_device();
     });
     if (rc != NB_OK) {
         g_create_error = h->last_error;
@@ -186,9 +204,68 @@ int nb_conv2d_forward(nb_plan_t plan, const float *x, float *y) {
         ConvPlan *p = static_cast<ConvPlan *>(plan);
         ForwardOpts o;
         o.x_nhwc = o.y_nhwc = p->d.layout == NB_LAYOUT_NHWC;
+        o.x_foreign = true;
         p->forward(x, y, o);
     });
 }
+int nb_conv2d_forward_fused(nb_plan_t plan, const float *x, float *y, const nb_conv2d_fusion_t *f) {
+    if (!plan) return NB_ERR_INVALID_ARG;
+    return guarded(plan->h, [&] {
+        NB_REQUIRE(plan->kind == NB_PLAN_CONV, "not a convolution plan");
+        NB_REQUIRE(f != nullptr, "null fusion descriptor");
+        NB_REQUIRE(!(f->residual && f->pool_out), "a convolution folds in a shortcut or a pooling layer, not both");
+        DeviceGuard g(plan->h->device);
+        ConvPlan *p = static_cast<ConvPlan *>(plan);
+        if (p->d.layout != NB_LAYOUT_NHWC) throw Error(NB_ERR_UNSUPPORTED, "fused layers need an NB_LAYOUT_NHWC plan");
+        ForwardOpts o;
+        o.x_nhwc = o.y_nhwc = true;
+        o.x_foreign = true;
+        if (f->residual) {
+            NB_REQUIRE(f->res_channels > 0 && f->res_height > 0 && f->res_width > 0, "residual: non-positive extent");
+            NB_REQUIRE(f->res_activation > NB_ACT_UNDEFINED && f->res_activation < NB_ACT_COUNT, "residual: undefined activation");
+            if (!p->can_fuse_shortcut(f->res_channels, f->res_height, f->res_width))
+                throw Error(NB_ERR_UNSUPPORTED, "this convolution cannot fold the shortcut in (it needs a tensor-core path, a "
+                                                "linear activation, channel counts divisible by 4 and a connection at "
+                                                "least as large as the output)");
+            o.residual = f->residual;
+            o.res_c = f->res_channels; o.res_h = f->res_height; o.res_w = f->res_width; o.res_act = f->res_activation;
+        }
+        if (f->pool_out) {
+            if (!p->can_fuse_pool())
+                throw Error(NB_ERR_UNSUPPORTED, "this convolution cannot fold the pooling in (it needs a tensor-core path, "
+                                                "even output extents and a filter count divisible by 4)");
+            o.pool_out = f->pool_out;
+        }
+        p->forward(x, f->pool_out ? nullptr : y, o);
+    });
+}
+int nb_plan_prepare(nb_plan_t plan) {
+    if (!plan) return NB_ERR_INVALID_ARG;
+    return guarded(plan->h, [&] {
+        DeviceGuard g(plan->h->device);
+        switch (plan->kind) {
+            case NB_PLAN_CONV: {
+                ConvPlan *p = static_cast<ConvPlan *>(plan);
+                ForwardOpts o;
+                o.x_nhwc = o.y_nhwc = p->d.layout == NB_LAYOUT_NHWC;
+                o.x_foreign = true;
+                p->reserve(o);
+                break;
+            }
+            case NB_PLAN_FC: {
+                ForwardOpts o;
+                o.x_foreign = true;
+                static_cast<FcPlan *>(plan)->reserve(o);
+                break;
+            }
+            case NB_PLAN_LSTM: static_cast<LstmPlan *>(plan)->reserve(true, false, false); break;
+            case NB_PLAN_RNN: static_cast<RnnPlan *>(plan)->reserve(false); break;
+            default: throw Error(NB_ERR_INVALID_ARG, "unknown plan kind");
+        }
+        NB_CHECK_CUDA(cudaStreamSynchronize(plan->h->stream));
+    });
+}
+size_t nb_workspace_size(nb_plan_t plan) { return plan ? plan->workspace_bytes() : 0; }
 int nb_plan_output_dims(nb_plan_t plan, int dims[3]) {
     if (!plan || !dims) return NB_ERR_INVALID_ARG;
     plan->output_dims(dims);
@@ -226,7 +303,9 @@ int nb_fc_forward(nb_plan_t plan, const float *x, float *y) {
     return guarded(plan->h, [&] {
         NB_REQUIRE(plan->kind == NB_PLAN_FC, "not a connected-layer plan");
         DeviceGuard g(plan->h->device);
-        static_cast<FcPlan *>(plan)->forward(x, y, ForwardOpts());
+        ForwardOpts o;
+        o.x_foreign = true;
+        static_cast<FcPlan *>(plan)->forward(x, y, o);
     });
 }
 
@@ -254,6 +333,34 @@ int nb_lstm_forward(nb_plan_t plan, const float *x, float *out, float *cell) {
         NB_REQUIRE(plan->kind == NB_PLAN_LSTM, "not an LSTM plan");
         DeviceGuard g(plan->h->device);
         static_cast<LstmPlan *>(plan)->forward(x, out, cell, false, nullptr);
+    });
+}
+
+int nb_rnn_plan_create(nb_handle_t h, const nb_rnn_desc_t *desc, nb_plan_t *plan) {
+    if (!h || !plan) return NB_ERR_INVALID_ARG;
+    *plan = nullptr;
+    return guarded(h, [&] {
+        NB_REQUIRE(desc != nullptr, "null descriptor");
+        DeviceGuard g(h->device);
+        *plan = new RnnPlan(h, *desc);
+    });
+}
+int nb_rnn_set_weights(nb_plan_t plan, const float *stream, size_t count, int mem) {
+    if (!plan) return NB_ERR_INVALID_ARG;
+    return guarded(plan->h, [&] {
+        NB_REQUIRE(plan->kind == NB_PLAN_RNN, "not an RNN plan");
+        NB_REQUIRE(mem == NB_MEM_HOST || mem == NB_MEM_DEVICE, "bad memory kind");
+        NB_REQUIRE(stream != nullptr, "null weight stream");
+        DeviceGuard g(plan->h->device);
+        static_cast<RnnPlan *>(plan)->set_weights(stream, count, mem);
+    });
+}
+int nb_rnn_forward(nb_plan_t plan, const float *x, float *out) {
+    if (!plan) return NB_ERR_INVALID_ARG;
+    return guarded(plan->h, [&] {
+        NB_REQUIRE(plan->kind == NB_PLAN_RNN, "not an RNN plan");
+        DeviceGuard g(plan->h->device);
+        static_cast<RnnPlan *>(plan)->forward(x, out, false, false);
     });
 }
 
@@ -396,18 +503,54 @@ int nb_network_forward(nb_network_t net, const float *input) {
 int nb_network_forward_host(nb_network_t net, const float *input_host, float *output_host) {
     if (!net) return NB_ERR_INVALID_ARG;
     return guarded(net->h, [&] {
-        NB_REQUIRE(input_host && output_host, "null host buffer");
         DeviceGuard g(net->h->device);
-        NB_CHECK_CUDA(cudaMemcpyAsync(net->input_dev.p, input_host, net->input_dev.n * sizeof(float),
-                                      cudaMemcpyHostToDevice, net->h->stream));
-        net->forward(net->input_dev.p);
-        net->layer_output(-1, output_host, NB_MEM_HOST);
+        net->submit(input_host, false, output_host);
+        net->wait();
     });
 }
+int nb_network_submit_host(nb_network_t net, const float *input_host, float *output_host) {
+    if (!net) return NB_ERR_INVALID_ARG;
+    return guarded(net->h, [&] {
+        DeviceGuard g(net->h->device);
+        net->submit(input_host, false, output_host);
+    });
+}
+int nb_network_submit_u8(nb_network_t net, const unsigned char *images_host, float *output_host) {
+    if (!net) return NB_ERR_INVALID_ARG;
+    return guarded(net->h, [&] {
+        DeviceGuard g(net->h->device);
+        net->submit(images_host, true, output_host);
+    });
+}
+int nb_network_wait(nb_network_t net) {
+    if (!net) return NB_ERR_INVALID_ARG;
+    return guarded(net->h, [&] {
+        DeviceGuard g(net->h->device);
+        net->wait();
+    });
+}
+int nb_network_forward_u8(nb_network_t net, const unsigned char *images_dev) {
+    if (!net) return NB_ERR_INVALID_ARG;
+    return guarded(net->h, [&] {
+        DeviceGuard g(net->h->device);
+        if (!net->weights_loaded && net->weight_count() > 0)
+            throw Error(NB_ERR_NO_WEIGHTS, "network forward before weights were loaded");
+        net->forward_u8(images_dev);
+    });
+}
+int nb_network_set_graph(nb_network_t net, int enable) {
+    if (!net) return NB_ERR_INVALID_ARG;
+    net->use_graph = enable != 0;
+    return NB_OK;
+}
+size_t nb_network_workspace_size(nb_network_t net) { return net ? net->workspace_bytes() : 0; }
 int nb_network_set_fusion(nb_network_t net, int enable) {
     if (!net) return NB_ERR_INVALID_ARG;
-    net->fuse = enable != 0;
-    return NB_OK;
+    return guarded(net->h, [&] {
+        DeviceGuard g(net->h->device);
+        net->fuse = enable != 0;
+        if (net->weights_loaded) net->prepare();
+    });
 }
 int nb_network_num_layers(nb_network_t net) { return net ? (int)net->layers.size() : -1; }
 int nb_network_layer_info(nb_network_t net, int index, nb_layer_info_t *info) {
@@ -444,9 +587,13 @@ size_t nb_network_logits_size(nb_network_t net) {
 size_t nb_network_input_size(nb_network_t net) { return net ? net->input_size * net->rows : 0; }
 int nb_network_destroy(nb_network_t net) {
     if (!net) return NB_ERR_INVALID_ARG;
+    int prev = -1;
+    cudaGetDevice(&prev);
     cudaSetDevice(net->h->device);
     cudaStreamSynchronize(net->h->stream);
+    if (net->copy_stream) cudaStreamSynchronize(net->copy_stream);
     delete net;
+    if (prev >= 0) cudaSetDevice(prev);
     return NB_OK;
 }
 

@@ -90,6 +90,17 @@ __global__ void __launch_bounds__(352, 1) conv3x3_halo_tcgen05_kernel(const __gr
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
+    // The last tap of a half reads up to two rows past the halo box (raster rows wt*(bh+2) and +1): they only feed
+    // junk accumulator rows, but they get a defined value (zero) once, here; no copy touches them afterwards.
+    {
+        const int box_rows = p.wt * (p.bh + 2);
+        constexpr int TAIL16 = 8 * 8;                   // eight rows of 128 bytes in 16-byte chunks
+        for (int i = threadIdx.x; i < A_RING * TAIL16; i += blockDim.x) {
+            const int s = i / TAIL16, c = i - s * TAIL16;
+            reinterpret_cast<float4 *>(a_ring + s * A_BYTES + box_rows * 128)[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -119,6 +130,16 @@ __global__ void __launch_bounds__(352, 1) conv3x3_halo_tcgen05_kernel(const __gr
                         if (++sb == B_RING) { sb = 0; pb ^= 1; }
                     }
                 }
+            }
+            // Tail: the issuers' last releases of every ring slot (mbarrier arrives that the tensor core performs when
+            // those MMAs retire) must have landed in this CTA's shared memory before the CTA may exit.
+            for (int i = 0; i < A_RING && ok; i++) {
+                ok = mbar_wait(&a_empty[sa], pa ^ 1, abort_flag, p.status);
+                if (++sa == A_RING) { sa = 0; pa ^= 1; }
+            }
+            for (int i = 0; i < B_RING && ok; i++) {
+                ok = mbar_wait(&b_empty[sb], pb ^ 1, abort_flag, p.status);
+                if (++sb == B_RING) { sb = 0; pb ^= 1; }
             }
         }
         __syncwarp();
@@ -217,6 +238,7 @@ __global__ void __launch_bounds__(352, 1) conv3x3_halo_tcgen05_kernel(const __gr
         __syncthreads();
     }
     if (warp == 1) {
+        __syncwarp();
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
     }
@@ -228,23 +250,26 @@ void encode(nb_handle_s *h, CUtensorMap *tm, const void *base, int rank, const c
     encode_tensor_map(h, tm, base, rank, dims, strides_bytes, box, es);
 }
 
-template <int BLOCK_N>
-void launch(nb_handle_s *h, const HaloParams &p) {
-    auto kern = conv3x3_halo_tcgen05_kernel<BLOCK_N>;
-    static bool configured = false;
-    if (!configured) {
-        NB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, HCfg<BLOCK_N>::SMEM_BYTES));
-        configured = true;
-    }
-    const int tiles = p.m_tiles * p.n_tiles;
-    kern<<<std::max(1, std::min(tiles, h->sm_count)), 352, HCfg<BLOCK_N>::SMEM_BYTES, h->stream>>>(p);
-    check_launch("conv3x3_halo_tcgen05_kernel");
-    count_launch(h);
-}
+typedef void (*HaloKernel)(const HaloParams);
+
+struct HaloLaunch : LaunchRecord {
+    HaloParams p;
+    HaloKernel kernel = nullptr;
+    int smem = 0, grid = 1;
+    double flops = 0;
+    std::string desc;
+};
 
 inline bool aligned16(const void *p) { return ((uintptr_t)p & 15) == 0; }
 
 }  // namespace
+
+void conv_halo_prepare_device() {
+    NB_CHECK_CUDA(cudaFuncSetAttribute(conv3x3_halo_tcgen05_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       HCfg<64>::SMEM_BYTES));
+    NB_CHECK_CUDA(cudaFuncSetAttribute(conv3x3_halo_tcgen05_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       HCfg<128>::SMEM_BYTES));
+}
 
 // Shapes this kernel takes: 3x3, stride 1, NHWC input with 32 <= C <= 128 and C % 4 == 0, TF32 mode,
 // output (or pooled output) addressable by TMA.
@@ -255,15 +280,18 @@ bool conv_halo_supported(const nb_handle_s *h, const GemmArgs &a) {
     if (a.Kc < 32 || a.Kc > 128 || (a.Kc % 4) || (a.ldb % 4) || (a.N % 4)) return false;
     if ((g.sw % 4) || (g.sh % 4) || (g.sn % 4) || !aligned16(a.a) || !aligned16(a.b)) return false;
     if (g.OW < 14 || g.OH < 8) return false;
-    if (a.addend && (a.res_stride <= 0 || (a.ld_addend % 4) || !aligned16(a.addend))) return false;
+    if (a.addend && (a.res_stride <= 0 || (a.ld_addend % 4) || !aligned16(a.addend) || a.addend_after_act)) return false;
     if (a.y_pool ? ((g.OW | g.OH) & 1) || !aligned16(a.y_pool) : (!a.y || !aligned16(a.y) || (a.ldy % 4))) return false;
     return true;
 }
 
-void conv_halo_tc(nb_handle_s *h, const GemmArgs &a) {
+namespace {
+
+std::unique_ptr<HaloLaunch> build_launch(nb_handle_s *h, const GemmArgs &a) {
     if (!conv_halo_supported(h, a)) throw Error(NB_ERR_UNSUPPORTED, "shape not supported by the 3x3 halo kernel");
     const ConvGeom &g = a.g;
-    HaloParams p;
+    std::unique_ptr<HaloLaunch> L(new HaloLaunch());
+    HaloParams &p = L->p;
     std::memset(&p, 0, sizeof p);
     p.bw = 14; p.wt = 16;
     p.halves = g.OH >= 16 ? 2 : 1;
@@ -284,6 +312,27 @@ void conv_halo_tc(nb_handle_s *h, const GemmArgs &a) {
     p.e.act = a.act; p.e.round_out = a.round_out_tf32 ? 1 : 0;
     p.e.y = a.y; p.e.ldy = a.ldy; p.e.tma_store = a.y_pool ? 0 : 1; p.e.pool = a.y_pool ? 1 : 0; p.e.N = a.N;
     p.status = h->d_status;
+
+    // every operand must lie inside the allocation its pointer belongs to
+    const long long F4 = 4, n32 = ((long long)a.N + 31) / 32 * 32;
+    // (TMA loads read the addresses of out-of-bounds box elements too, although those arrive as zeros)
+    {
+        const long long cmax = (long long)p.c_blocks * BLOCK_K - 1;
+        const long long wmax = (long long)(p.tiles_w - 1) * p.bw - p.pad + p.wt - 1;
+        const long long hmax = (long long)(p.tiles_h - 1) * p.bh - p.pad + p.bh + 1;
+        const long long lo = -(long long)p.pad * (g.sw + g.sh);
+        const long long hi = wmax * g.sw + hmax * g.sh + (long long)(g.batch - 1) * g.sn + cmax + 1;
+        check_extent(h, a.a, lo * F4, hi * F4, "A operand (with the out-of-bounds elements its halo boxes cover)");
+        const long long rows = 8LL * a.N + (long long)p.n_tiles * block_n;
+        check_extent(h, a.b, 0, ((rows - 1) * a.ldb + cmax + 1) * F4, "B operand (with the rows past the last filter its boxes cover)");
+    }
+    if (a.scale) check_extent(h, a.scale, 0, n32 * F4, "epilogue scale vector (padded to 32 columns)");
+    if (a.shift) check_extent(h, a.shift, 0, n32 * F4, "epilogue shift vector (padded to 32 columns)");
+    if (a.addend)
+        check_extent(h, a.addend, 0, (((long long)g.batch * a.res_h * a.res_w - 1) * a.ld_addend + a.res_c) * F4, "addend");
+    if (a.y_pool) check_extent(h, a.y_pool, 0, (long long)g.batch * (g.OH / 2) * (g.OW / 2) * a.N * F4, "pooled output");
+    else check_extent(h, a.y, 0, (((long long)g.batch * g.OH * g.OW - 1) * a.ldy + a.N) * F4, "output");
+
     {   // A halo: dims {C, W, H, N}, box {32, bw+2, bh+2, 1}
         cuuint64_t dims[4] = {(cuuint64_t)a.Kc, (cuuint64_t)g.W, (cuuint64_t)g.H, (cuuint64_t)g.batch};
         cuuint64_t strides[3] = {(cuuint64_t)g.sw * 4, (cuuint64_t)g.sh * 4, (cuuint64_t)g.sn * 4};
@@ -309,9 +358,36 @@ void conv_halo_tc(nb_handle_s *h, const GemmArgs &a) {
         cuuint32_t bx[4] = {32, (cuuint32_t)p.bw, (cuuint32_t)p.rows_half, 1};
         encode(h, &p.tm_y, a.y, 4, dims, strides, bx);
     }
-    ProfileScope prof(h, 2, a.algo_flops > 0 ? a.algo_flops : 2.0 * (double)a.M * a.N * a.Kc * 9);
-    if (block_n == 128) launch<128>(h, p);
-    else launch<64>(h, p);
+    const int tiles = p.m_tiles * p.n_tiles;
+    L->grid = std::max(1, std::min(tiles, h->sm_count));
+    if (block_n == 128) { L->kernel = conv3x3_halo_tcgen05_kernel<128>; L->smem = HCfg<128>::SMEM_BYTES; }
+    else { L->kernel = conv3x3_halo_tcgen05_kernel<64>; L->smem = HCfg<64>::SMEM_BYTES; }
+    L->flops = a.algo_flops > 0 ? a.algo_flops : 2.0 * (double)a.M * a.N * a.Kc * 9;
+    L->desc = " [3x3 halo C=" + std::to_string(a.Kc) + " N=" + std::to_string(a.N) + " out=" + std::to_string(g.OW) + "x" +
+              std::to_string(g.OH) + "x" + std::to_string(g.batch) + " block_n=" + std::to_string(block_n) +
+              (a.y_pool ? " pool" : "") + (a.addend ? " addend" : "") + "]";
+    return L;
+}
+
+}  // namespace
+
+void conv_halo_tc(nb_handle_s *h, const GemmArgs &a) {
+    std::string key = gemm_args_key(a, 'H', 0);
+    auto it = h->launch_cache.find(key);
+    if (it == h->launch_cache.end()) {
+        if (h->launch_cache.size() > 4096) h->launch_cache.clear();
+        it = h->launch_cache.emplace(std::move(key), build_launch(h, a)).first;
+    }
+    const HaloLaunch &L = static_cast<const HaloLaunch &>(*it->second);
+    ProfileScope prof(h, 2, L.flops);
+    L.kernel<<<L.grid, 352, L.smem, h->stream>>>(L.p);
+    try {
+        check_launch("conv3x3_halo_tcgen05_kernel");
+    } catch (const Error &err) {
+        throw Error(err.code, std::string(err.what()) + L.desc);
+    }
+    count_launch(h);
+    prof.finish();
 }
 
 }  // namespace nb

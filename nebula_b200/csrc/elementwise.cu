@@ -23,6 +23,30 @@ void check_launch(const char *what) {
     if (e != cudaSuccess) throw Error(NB_ERR_CUDA, std::string(what) + " launch: " + cudaGetErrorString(e));
 }
 
+void check_extent(nb_handle_s *h, const void *p, long long lo_bytes, long long hi_bytes, const char *what) {
+    if (!h->get_address_range || !p || hi_bytes <= lo_bytes) return;
+    const uintptr_t q = (uintptr_t)p, a = q + lo_bytes, b = q + hi_bytes;
+    auto it = h->known_ranges.upper_bound(q);
+    if (it != h->known_ranges.begin()) {
+        --it;
+        if (q < it->second && a >= it->first && b <= it->second) return;
+    }
+    // not covered by what was seen before (or that allocation has been replaced since): ask the driver
+    CUdeviceptr base = 0;
+    size_t size = 0;
+    if (h->get_address_range(&base, &size, (CUdeviceptr)q) != CUDA_SUCCESS || !size) return;   // not an allocation
+    const uintptr_t lo = (uintptr_t)base, hi = lo + size;
+    for (auto k = h->known_ranges.begin(); k != h->known_ranges.end();)     // forget stale overlapping entries
+        k = (k->first < hi && k->second > lo) ? h->known_ranges.erase(k) : std::next(k);
+    if (h->known_ranges.size() > 4096) h->known_ranges.clear();
+    h->known_ranges[lo] = hi;
+    if (a < lo || b > hi)
+        throw Error(NB_ERR_INVALID_ARG, std::string(what) + ": the launch would touch bytes [" + std::to_string(lo_bytes) + ", " +
+                                            std::to_string(hi_bytes) + ") from its pointer, but the allocation it lies in holds [" +
+                                            std::to_string((long long)lo - (long long)q) + ", " +
+                                            std::to_string((long long)hi - (long long)q) + ")");
+}
+
 namespace {
 
 constexpr int TPB = 256;
@@ -300,6 +324,38 @@ __global__ void rowwin_input_kernel(const float *x, float4 *dst, int N, int C, i
     }
 }
 
+// Decoded 8-bit images [N][H][W][C] (C = 3: BGR as OpenCV holds them, or 1) -> the network input, with the reference's
+// conversion (models/networks/convolutional.cc:386-398): value / 255.0 evaluated in double and stored as float, planes 0
+// and 2 swapped for three channels.  Two destinations: the reference's own fp32 NCHW batch, or (rowwin != 0) the
+// first convolution's row-window tensor [N][H][Wp][4] directly (zero pixels left and right, zero in channels >= C).
+__global__ void u8_pack_kernel(const unsigned char *img, float *dst, int N, int C, int H, int W, int rowwin, int Wp, int pad,
+                               int round, size_t total) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        if (rowwin) {       // one thread per padded pixel
+            const int pcol = (int)(i % Wp);
+            const size_t nh = i / Wp;
+            const int iw = pcol - pad;
+            float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            if (iw >= 0 && iw < W) {
+                const unsigned char *px = img + (nh * W + iw) * C;
+                for (int c = 0; c < C; c++) {
+                    const float t = (float)((double)px[C == 3 ? 2 - c : c] / 255.0);
+                    v[c] = round ? round_tf32(t) : t;
+                }
+            }
+            reinterpret_cast<float4 *>(dst)[i] = make_float4(v[0], v[1], v[2], v[3]);
+        } else {            // one thread per output element of [N][C][H][W]
+            size_t t = i;
+            const int w = (int)(t % W); t /= W;
+            const int hh = (int)(t % H); t /= H;
+            const int c = (int)(t % C);
+            const size_t n = t / C;
+            dst[i] = (float)((double)img[((n * H + hh) * W + w) * C + (C == 3 ? 2 - c : c)] / 255.0);
+        }
+    }
+}
+
 // ---------------------------------------------------------- weight layouts
 // OIHW [F][C][k][k] -> [tap][F][Cp], zero for c >= C
 __global__ void weight_relayout_kernel(const float *w, float *dst, int F, int C, int k, int Cp, size_t total) {
@@ -392,6 +448,22 @@ __global__ void sgemm_kernel(int ta, int tb, int M, int N, int K, float alpha, c
 }
 
 }  // namespace
+
+// Loads the code of every kernel of this file on the current device (a kernel's code is otherwise loaded by its
+// first launch, in the middle of the first forward pass).
+void elementwise_prepare_device() {
+    cudaFuncAttributes fa;
+    const void *kernels[] = {
+        (const void *)activation_kernel, (const void *)bias_kernel, (const void *)bn_normalize_kernel,
+        (const void *)bn_scale_kernel, (const void *)softmax_kernel, (const void *)transpose_kernel,
+        (const void *)round_tf32_kernel, (const void *)split_tf32_kernel, (const void *)pool_kernel<true>,
+        (const void *)pool_kernel<false>, (const void *)pool_nhwc4_kernel, (const void *)shortcut_kernel<true>,
+        (const void *)shortcut_kernel<false>, (const void *)weight_pack_kernel, (const void *)weight_rowwin_kernel,
+        (const void *)rowwin_input_kernel, (const void *)weight_relayout_kernel, (const void *)fc_permute_kernel,
+        (const void *)splitk_reduce_kernel, (const void *)lstm_cell_kernel, (const void *)sgemm_kernel,
+        (const void *)u8_pack_kernel};
+    for (const void *k : kernels) NB_CHECK_CUDA(cudaFuncGetAttributes(&fa, k));
+}
 
 // ---------------------------------------------------------------- launchers
 void launch_sgemm(nb_handle_s *h, bool ta, bool tb, int M, int N, int K, float alpha, const float *A, int lda,
@@ -521,6 +593,14 @@ void launch_rowwin_input(nb_handle_s *h, const float *x, float *dst, int N, int 
     rowwin_input_kernel<<<grid_for(total, h), TPB, 0, h->stream>>>(x, reinterpret_cast<float4 *>(dst), N, C, H, W, Wp, pad,
                                                                   nhwc_in ? 1 : 0, round ? 1 : 0, total);
     check_launch("rowwin_input_kernel");
+    count_launch(h);
+}
+void launch_u8_pack(nb_handle_s *h, const unsigned char *img, float *dst, int N, int C, int H, int W, bool rowwin, int Wp,
+                    int pad, bool round) {
+    const size_t total = rowwin ? (size_t)N * H * Wp : (size_t)N * C * H * W;
+    if (!total) return;
+    u8_pack_kernel<<<grid_for(total, h), TPB, 0, h->stream>>>(img, dst, N, C, H, W, rowwin ? 1 : 0, Wp, pad, round ? 1 : 0, total);
+    check_launch("u8_pack_kernel");
     count_launch(h);
 }
 void launch_weight_relayout(nb_handle_s *h, const float *w, float *dst, int F, int C, int k, int Cp) {

@@ -23,7 +23,7 @@ struct SimtParams {
     int M, N, Kc, taps;
     const float *scale, *shift, *addend;
     long ld_addend;
-    int act, round_out;
+    int act, round_out, addend_post;
     float *y;
     long ldy;
 };
@@ -98,8 +98,9 @@ __global__ void __launch_bounds__(256) gemm_fp32_simt_kernel(const SimtParams p)
             float x = acc[i][j];
             if (p.scale) x *= p.scale[n];
             if (p.shift) x += p.shift[n];
-            if (p.addend) x += p.addend[m * p.ld_addend + n];
+            if (p.addend && !p.addend_post) x += p.addend[m * p.ld_addend + n];
             x = apply_activation_fast(x, p.act);
+            if (p.addend && p.addend_post) x += p.addend[m * p.ld_addend + n];
             p.y[m * p.ldy + n] = p.round_out ? round_tf32(x) : x;
         }
     }
@@ -120,13 +121,14 @@ void gemm_simt(nb_handle_s *h, const GemmArgs &a) {
     }
     p.ldb = a.ldb; p.M = a.M; p.N = a.N; p.Kc = a.Kc; p.taps = p.g.ksize * p.g.ksize;
     p.scale = a.scale; p.shift = a.shift; p.addend = a.addend; p.ld_addend = a.ld_addend;
-    p.act = a.act; p.round_out = a.round_out_tf32 ? 1 : 0;
+    p.act = a.act; p.round_out = a.round_out_tf32 ? 1 : 0; p.addend_post = a.addend_after_act ? 1 : 0;
     p.y = a.y; p.ldy = a.ldy;
     ProfileScope prof(h, 1, 2.0 * (double)a.M * a.N * a.Kc * p.taps);
     dim3 grid((unsigned)((a.M + TM - 1) / TM), (unsigned)((a.N + TN - 1) / TN));
     gemm_fp32_simt_kernel<<<grid, 256, 0, h->stream>>>(p);
     check_launch("gemm_fp32_simt_kernel");
     count_launch(h);
+    prof.finish();
 }
 
 void gemm(nb_handle_s *h, const GemmArgs &a) {

@@ -137,6 +137,20 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
+    // A pixel box of fewer than 128 rows leaves the tail rows of every A stage unwritten by TMA, and the MMA reads
+    // all 128: those rows only feed accumulator rows that are never stored, but they are given a defined value
+    // (zero) once, here; no copy touches them afterwards.
+    {
+        const int box_rows = p.gather ? BLOCK_M : p.bw * p.bh * p.bn;
+        if (box_rows < BLOCK_M) {
+            const int tail16 = (BLOCK_M - box_rows) * 8;          // 16-byte chunks per stage tail
+            for (int i = threadIdx.x; i < STAGES * tail16; i += blockDim.x) {
+                const int s = i / tail16, c = i - s * tail16;
+                reinterpret_cast<float4 *>(smem + s * C::STAGE_BYTES + box_rows * 128)[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
+    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -181,6 +195,12 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
                     }
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
+            }
+            // Tail: the MMA warp's last release of every stage (an mbarrier arrive that the tensor core performs
+            // when those MMAs retire) must have landed in this CTA's shared memory before the CTA may exit.
+            for (int i = 0; i < STAGES && ok; i++) {
+                ok = mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status);
+                if (++stage == STAGES) { stage = 0; phase ^= 1; }
             }
         }
         __syncwarp();
@@ -369,8 +389,8 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
 #pragma unroll
                     for (int e = 0; e < 4; e++) {
                         if (THREE) {
-                            v[e] = __uint_as_float(__float_as_uint(x[4 * j + e]) & 0xFFFFE000u);
-                            lo[e] = x[4 * j + e] - v[e];
+                            v[e] = round_tf32(x[4 * j + e]);
+                            lo[e] = round_tf32(x[4 * j + e] - v[e]);
                         } else {
                             v[e] = p.ground ? round_tf32(x[4 * j + e]) : x[4 * j + e];
                         }
@@ -385,9 +405,9 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
         }
     } else if (THREE) {
         // ---------------------------------------------- hi/lo operand splitter
-        // hi = the TF32 the tensor core would read (low 13 mantissa bits cleared),
-        // lo = x - hi (exact in fp32).  Element positions are kept, so the swizzled
-        // tile layout written by TMA is preserved.
+        // hi = RN_tf32(x), lo = RN_tf32(x - hi), the same split the weights get at load: both terms are exact TF32
+        // values, so the tensor core's truncation of its operands changes nothing and the split has no bias.
+        // Element positions are kept, so the swizzled tile layout written by TMA is preserved.
         const int t = threadIdx.x - 320;        // 0..127
         int stage = 0;
         uint32_t phase = 0;
@@ -400,10 +420,10 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
 #pragma unroll
                 for (int i = 0; i < A_STAGE_BYTES / 16 / 128; i++) {
                     float4 x = a[i * 128 + t], h, l;
-                    h.x = __uint_as_float(__float_as_uint(x.x) & 0xFFFFE000u); l.x = x.x - h.x;
-                    h.y = __uint_as_float(__float_as_uint(x.y) & 0xFFFFE000u); l.y = x.y - h.y;
-                    h.z = __uint_as_float(__float_as_uint(x.z) & 0xFFFFE000u); l.z = x.z - h.z;
-                    h.w = __uint_as_float(__float_as_uint(x.w) & 0xFFFFE000u); l.w = x.w - h.w;
+                    h.x = round_tf32(x.x); l.x = round_tf32(x.x - h.x);
+                    h.y = round_tf32(x.y); l.y = round_tf32(x.y - h.y);
+                    h.z = round_tf32(x.z); l.z = round_tf32(x.z - h.z);
+                    h.w = round_tf32(x.w); l.w = round_tf32(x.w - h.w);
                     a[i * 128 + t] = h;
                     a_lo[i * 128 + t] = l;
                 }
@@ -424,6 +444,7 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
         __syncthreads();
     }
     if (warp == 1) {
+        __syncwarp();
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
                      "r"((uint32_t)C::TMEM_COLS)
@@ -434,9 +455,12 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
 // ---------------------------------------------------------------- host side
 struct Box { int bw, bh, bn; };
 
-// Chooses the (bw x bh x bn) pixel box (<= 128 rows) that wastes the fewest MMA rows.
+// Chooses the (bw x bh x bn) pixel box (<= 128 rows) that wastes the fewest MMA rows.  Among equally full boxes the
+// one that spans the fewest images wins (its rows are the longest contiguous runs in memory), then the widest.
 // bn_divides: the images of a box must not run past the batch (split-K slabs follow each other in y)
-Box choose_box(int OW, int OH, int NB, int stride, bool even, bool bn_divides) {
+// image_bytes: size of one image of the A tensor -- a box that runs past the batch makes the load unit read that many
+// bytes per missing image behind the tensor, so such boxes are only taken while that stays small
+Box choose_box(int OW, int OH, int NB, int stride, bool even, bool bn_divides, double image_bytes) {
     Box best{1, 1, 1};
     double best_eff = -1;
     const int max_dim = 256 / std::max(1, stride);     // TMA box extent limit (elements traversed)
@@ -445,12 +469,11 @@ Box choose_box(int OW, int OH, int NB, int stride, bool even, bool bn_divides) {
         for (int bh = 1; bh <= std::min({OH, rem, max_dim}); bh++) {
             int bn = std::min({NB, 128 / (bw * bh), 256});
             if (bn < 1) continue;
-            while (bn_divides && NB % bn) bn--;
+            while ((bn_divides || (double)(((NB + bn - 1) / bn) * bn - NB) * image_bytes > 4e6) && NB % bn) bn--;
             if (even && ((bw | bh) & 1)) continue;      // 2x2 pooling windows must not straddle tiles
             auto eff1 = [](int ext, int b) { return (double)ext / ((double)((ext + b - 1) / b) * b); };
             double eff = eff1(OW, bw) * eff1(OH, bh) * eff1(NB, bn) * (double)(bw * bh * bn) / 128.0;
-            // prefer wider boxes on ties (longer contiguous runs per TMA request)
-            eff += 1e-6 * bw;
+            eff += 1e-6 * bw + 1e-4 / bn;
             if (eff > best_eff) { best_eff = eff; best = Box{bw, bh, bn}; }
         }
     }
@@ -462,46 +485,68 @@ void encode(nb_handle_s *h, CUtensorMap *tm, const void *base, int rank, const c
     encode_tensor_map(h, tm, base, rank, dims, strides_bytes, box, elem_strides);
 }
 
+typedef void (*TcKernel)(const TcParams);
+
+struct Variant { TcKernel kernel; int smem; };
+
 template <int BLOCK_N, bool THREE, bool PROMOTE>
-void launch(nb_handle_s *h, const TcParams &p) {
-    using C = Cfg<BLOCK_N, THREE>;
-    auto kern = gemm_tf32_tcgen05_kernel<BLOCK_N, THREE, PROMOTE>;
-    static bool configured = false;
-    if (!configured) {
-        NB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
-        configured = true;
-    }
-    const int tiles = p.m_tiles * p.n_tiles * p.k_splits;
-    const int grid = std::max(1, std::min(tiles, h->sm_count));
-    const int threads = (THREE || p.gather) ? 448 : 320;
-    kern<<<grid, threads, C::SMEM_BYTES, h->stream>>>(p);
-    check_launch("gemm_tf32_tcgen05_kernel");
-    count_launch(h);
-}
+Variant variant() { return {gemm_tf32_tcgen05_kernel<BLOCK_N, THREE, PROMOTE>, Cfg<BLOCK_N, THREE>::SMEM_BYTES}; }
+
+// index: [three][promote][block_n: 0 = 64, 1 = 128, 2 = 256]; absent combinations are null
+const Variant VARIANTS[2][2][3] = {
+    {{variant<64, false, false>(), variant<128, false, false>(), variant<256, false, false>()},
+     {variant<64, false, true>(), variant<128, false, true>(), {nullptr, 0}}},
+    {{{nullptr, 0}, {nullptr, 0}, {nullptr, 0}},
+     {variant<64, true, true>(), variant<128, true, true>(), {nullptr, 0}}},
+};
+
+// One worked-out launch: kernel parameters (tile geometry, tensor maps), kernel variant, grid.
+struct TcLaunch : LaunchRecord {
+    TcParams p;
+    Variant v;
+    int grid = 1, threads = 320;
+    double flops = 0;
+    std::string desc;       // names the launch in error messages
+};
 
 inline bool aligned16(const void *p) { return ((uintptr_t)p & 15) == 0; }
 
 }  // namespace
 
+void gemm_tc_prepare_device() {
+    for (auto &t : VARIANTS)
+        for (auto &pr : t)
+            for (auto &v : pr)
+                if (v.kernel) NB_CHECK_CUDA(cudaFuncSetAttribute(v.kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, v.smem));
+}
+
 void encode_tensor_map(nb_handle_s *h, CUtensorMap *tm, const void *base, int rank, const cuuint64_t *dims,
                        const cuuint64_t *strides_bytes, const cuuint32_t *box, const cuuint32_t *elem_strides) {
-    std::string key;
-    key.reserve(160);
-    key.append((const char *)&base, sizeof base);
-    key.append((const char *)&rank, sizeof rank);
-    key.append((const char *)dims, sizeof(cuuint64_t) * rank);
-    key.append((const char *)strides_bytes, sizeof(cuuint64_t) * (rank - 1));
-    key.append((const char *)box, sizeof(cuuint32_t) * rank);
-    key.append((const char *)elem_strides, sizeof(cuuint32_t) * rank);
-    auto it = h->tensor_maps.find(key);
-    if (it != h->tensor_maps.end()) { *tm = it->second; return; }
     CUresult r = h->encode_tiled(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, const_cast<void *>(base), dims,
                                  strides_bytes, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) throw Error(NB_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
-    if (h->tensor_maps.size() > 8192) h->tensor_maps.clear();
-    h->tensor_maps.emplace(std::move(key), *tm);
+}
+
+std::string gemm_args_key(const GemmArgs &a, char tag, int extra) {
+    std::string k;
+    k.reserve(320);
+    k.push_back(tag);
+    key_add(k, extra);
+    key_add(k, a.a); key_add(k, a.a_is_conv); key_add(k, a.lda);
+    const ConvGeom &g = a.g;
+    key_add(k, g.batch); key_add(k, g.C); key_add(k, g.H); key_add(k, g.W); key_add(k, g.OH); key_add(k, g.OW);
+    key_add(k, g.ksize); key_add(k, g.stride); key_add(k, g.pad); key_add(k, g.ksize_w); key_add(k, g.pad_w);
+    key_add(k, g.sn); key_add(k, g.sc); key_add(k, g.sh); key_add(k, g.sw);
+    key_add(k, a.a_gather); key_add(k, a.b); key_add(k, a.b_lo); key_add(k, a.ldb);
+    key_add(k, a.M); key_add(k, a.N); key_add(k, a.Kc);
+    key_add(k, a.scale); key_add(k, a.shift); key_add(k, a.addend); key_add(k, a.ld_addend); key_add(k, a.addend_after_act);
+    key_add(k, a.res_stride); key_add(k, a.res_c); key_add(k, a.res_h); key_add(k, a.res_w);
+    key_add(k, a.act); key_add(k, a.round_out_tf32); key_add(k, a.y); key_add(k, a.ldy); key_add(k, a.y_pool);
+    key_add(k, a.lstm_H); key_add(k, a.lstm_c_prev); key_add(k, a.lstm_c); key_add(k, a.lstm_h); key_add(k, a.lstm_h_round);
+    key_add(k, a.split_k); key_add(k, a.block_n_hint); key_add(k, a.algo_flops);
+    return k;
 }
 
 bool gemm_tc_supported(const nb_handle_s *h, const GemmArgs &a) {
@@ -519,11 +564,16 @@ bool gemm_tc_supported(const nb_handle_s *h, const GemmArgs &a) {
     return true;
 }
 
-void gemm_tc(nb_handle_s *h, const GemmArgs &a, bool three_pass) {
+namespace {
+
+// Works out one launch: tiling, kernel variant, tensor maps; checks that every operand's extent lies inside the
+// device allocation its pointer belongs to.
+std::unique_ptr<TcLaunch> build_launch(nb_handle_s *h, const GemmArgs &a, bool three_pass) {
     if (!gemm_tc_supported(h, a)) throw Error(NB_ERR_UNSUPPORTED, "operands do not satisfy the TMA layout rules");
     if (a.y_pool && a.a_gather) throw Error(NB_ERR_UNSUPPORTED, "fused pooling is not available with the gathered A operand");
     if (three_pass && !a.b_lo) throw Error(NB_ERR_INVALID_ARG, "three-pass GEMM needs the low-order weight split");
-    TcParams p;
+    std::unique_ptr<TcLaunch> L(new TcLaunch());
+    TcParams &p = L->p;
     std::memset(&p, 0, sizeof p);
 
     ConvGeom g;
@@ -543,7 +593,7 @@ void gemm_tc(nb_handle_s *h, const GemmArgs &a, bool three_pass) {
     const int ksize_w = g.ksize_w > 0 ? g.ksize_w : g.ksize;
     const int taps = g.ksize * ksize_w;
     const bool pool = a.y_pool != nullptr;
-    Box box = choose_box(g.OW, g.OH, g.batch, g.stride, pool, S > 1);
+    Box box = choose_box(g.OW, g.OH, g.batch, g.stride, pool, S > 1, (double)g.sn * 4.0);
     p.bw = box.bw; p.bh = box.bh; p.bn = box.bn;
     p.tiles_w = (g.OW + box.bw - 1) / box.bw;
     p.tiles_h = (g.OH + box.bh - 1) / box.bh;
@@ -564,6 +614,9 @@ void gemm_tc(nb_handle_s *h, const GemmArgs &a, bool three_pass) {
     p.e.addend_vec = a.addend && aligned16(a.addend) && (a.ld_addend % 4) == 0;
     p.e.addend_cols = a.addend ? (a.res_stride > 0 ? a.res_c : a.N) : 0;
     p.e.res_stride = a.addend ? a.res_stride : 0; p.e.res_h = a.res_h; p.e.res_w = a.res_w;
+    p.e.addend_post = (a.addend && a.addend_after_act) ? 1 : 0;
+    if (a.lstm_H > 0 && a.act != NB_ACT_LINEAR && !p.e.addend_post)
+        throw Error(NB_ERR_INVALID_ARG, "LSTM epilogue: a non-linear gate activation needs the addend added after it");
     p.e.y = a.y; p.e.ldy = a.ldy;
     p.e.tma_store = a.y && aligned16(a.y) && (a.ldy % 4) == 0;
     if (S > 1 && !p.e.tma_store) throw Error(NB_ERR_INVALID_ARG, "split-K needs a 16-byte aligned output with ldy % 4 == 0");
@@ -622,6 +675,51 @@ void gemm_tc(nb_handle_s *h, const GemmArgs &a, bool three_pass) {
         p.gH = a.g.H; p.gW = a.g.W; p.gOH = a.g.OH; p.gOW = a.g.OW; p.gstride = a.g.stride; p.gM = a.M;
         p.ground = three_pass ? 0 : 1;
     }
+
+    // ---- every operand must lie inside the allocation its pointer belongs to.  For the operands TMA loads, that
+    // includes what the boxes at out-of-bounds coordinates cover: such elements arrive as zeros, but the load unit
+    // still reads the addresses they map to (rows above the first image, past the last one, past the last filter).
+    const long long F4 = 4;
+    const long long n32 = ((long long)a.N + 31) / 32 * 32;
+    const long long cmax = (long long)p.c_blocks * BLOCK_K - 1;
+    if (gather) {
+        const long long last = (long long)(a.g.batch - 1) * a.g.sn + (long long)(a.g.H - 1) * a.g.sh +
+                               (long long)(a.g.W - 1) * a.g.sw + (long long)(a.g.C - 1) * a.g.sc;
+        check_extent(h, a.a, 0, (last + 1) * F4, "gathered input tensor");
+    } else {
+        const long long wmin = -(long long)p.pad_w, hmin = -(long long)p.pad_h;
+        const long long wmax = (long long)(p.tiles_w - 1) * box.bw * g.stride + wmin + (ksize_w - 1) + (long long)box.bw * g.stride - 1;
+        const long long hmax = (long long)(p.tiles_h - 1) * box.bh * g.stride + hmin + (g.ksize - 1) + (long long)box.bh * g.stride - 1;
+        const long long nmax = (long long)p.tiles_n * box.bn - 1;
+        const long long lo = std::min(wmin, 0LL) * g.sw + std::min(hmin, 0LL) * g.sh;
+        const long long hi = wmax * g.sw + hmax * g.sh + nmax * g.sn + cmax + 1;
+        check_extent(h, a.a, lo * F4, hi * F4, "A operand (with the out-of-bounds elements its boxes cover)");
+    }
+    {
+        const long long rows = (long long)(taps - 1) * a.N + (long long)p.n_tiles * block_n;
+        const long long b_floats = (rows - 1) * a.ldb + cmax + 1;
+        check_extent(h, a.b, 0, b_floats * F4, "B operand (with the rows past the last filter its boxes cover)");
+        if (three_pass) check_extent(h, a.b_lo, 0, b_floats * F4, "low-order B operand");
+    }
+    if (a.scale) check_extent(h, a.scale, 0, n32 * F4, "epilogue scale vector (padded to 32 columns)");
+    if (a.shift) check_extent(h, a.shift, 0, n32 * F4, "epilogue shift vector (padded to 32 columns)");
+    if (a.addend) {
+        const long long fl = a.res_stride > 0
+            ? ((long long)g.batch * a.res_h * a.res_w - 1) * a.ld_addend + a.res_c
+            : ((long long)a.M - 1) * a.ld_addend + a.N;
+        check_extent(h, a.addend, 0, fl * F4, "addend");
+    }
+    if (a.y && !pool && !a.lstm_H)
+        check_extent(h, a.y, 0, (((long long)S * a.M - 1) * a.ldy + a.N) * F4, "output");
+    if (pool) check_extent(h, a.y_pool, 0, (long long)g.batch * (g.OH / 2) * (g.OW / 2) * a.N * F4, "pooled output");
+    if (a.lstm_H > 0) {
+        const long long fl = (long long)a.M * a.lstm_H * F4;
+        if (a.lstm_c_prev) check_extent(h, a.lstm_c_prev, 0, fl, "previous cell state");
+        check_extent(h, a.lstm_c, 0, fl, "cell state");
+        check_extent(h, a.lstm_h, 0, fl, "hidden state");
+        if (a.lstm_h_round) check_extent(h, a.lstm_h_round, 0, fl, "rounded hidden state");
+    }
+
     if (!gather) {   // A: dims {C, W, H, N}
         cuuint64_t dims[4] = {(cuuint64_t)kc, (cuuint64_t)g.W, (cuuint64_t)g.H, (cuuint64_t)g.batch};
         cuuint64_t strides[3] = {(cuuint64_t)g.sw * 4, (cuuint64_t)g.sh * 4, (cuuint64_t)g.sn * 4};
@@ -657,29 +755,40 @@ void gemm_tc(nb_handle_s *h, const GemmArgs &a, bool three_pass) {
         encode(h, &p.tm_yp, a.y_pool, 4, dims, strides, bx, es);
     }
 
-    ProfileScope prof(h, 0, a.algo_flops > 0 ? a.algo_flops : 2.0 * (double)a.M * a.N * a.Kc * taps);
-    try {
-        if (three_pass) {
-            if (block_n == 128) launch<128, true, true>(h, p);
-            else launch<64, true, true>(h, p);
-        } else if (promote) {
-            if (block_n == 128) launch<128, false, true>(h, p);
-            else launch<64, false, true>(h, p);
-        } else {
-            if (block_n == 256) launch<256, false, false>(h, p);
-            else if (block_n == 128) launch<128, false, false>(h, p);
-            else launch<64, false, false>(h, p);
-        }
-    } catch (const Error &err) {
-        // name the launch: an asynchronous fault is otherwise hard to place
-        throw Error(err.code, std::string(err.what()) + " [M=" + std::to_string(a.M) + " N=" + std::to_string(a.N) + " K=" +
-                                  std::to_string(a.Kc) + " taps=" + std::to_string(taps) + " stride=" + std::to_string(g.stride) +
-                                  " out=" + std::to_string(g.OW) + "x" + std::to_string(g.OH) + "x" + std::to_string(g.batch) +
-                                  " box=" + std::to_string(box.bw) + "x" + std::to_string(box.bh) + "x" + std::to_string(box.bn) +
-                                  " block_n=" + std::to_string(block_n) + " splits=" + std::to_string(S) +
-                                  (gather ? " gather" : "") + (three_pass ? " 3xtf32" : "") + (pool ? " pool" : "") +
-                                  (a.addend ? " addend" : "") + (a.lstm_H ? " lstm" : "") + "]");
+    L->v = VARIANTS[three_pass ? 1 : 0][promote ? 1 : 0][block_n == 256 ? 2 : (block_n == 128 ? 1 : 0)];
+    if (!L->v.kernel) throw Error(NB_ERR_UNSUPPORTED, "no tensor-core kernel variant for this tile width");
+    const int tiles = p.m_tiles * p.n_tiles * p.k_splits;
+    L->grid = std::max(1, std::min(tiles, h->sm_count));
+    L->threads = (three_pass || gather) ? 448 : 320;
+    L->flops = a.algo_flops > 0 ? a.algo_flops : 2.0 * (double)a.M * a.N * a.Kc * taps;
+    L->desc = " [M=" + std::to_string(a.M) + " N=" + std::to_string(a.N) + " K=" + std::to_string(a.Kc) + " taps=" +
+              std::to_string(taps) + " stride=" + std::to_string(g.stride) + " out=" + std::to_string(g.OW) + "x" +
+              std::to_string(g.OH) + "x" + std::to_string(g.batch) + " box=" + std::to_string(box.bw) + "x" +
+              std::to_string(box.bh) + "x" + std::to_string(box.bn) + " block_n=" + std::to_string(block_n) +
+              " splits=" + std::to_string(S) + (gather ? " gather" : "") + (three_pass ? " 3xtf32" : "") +
+              (pool ? " pool" : "") + (a.addend ? " addend" : "") + (a.lstm_H ? " lstm" : "") + "]";
+    return L;
+}
+
+}  // namespace
+
+void gemm_tc(nb_handle_s *h, const GemmArgs &a, bool three_pass) {
+    std::string key = gemm_args_key(a, 'G', three_pass ? 1 : 0);
+    auto it = h->launch_cache.find(key);
+    if (it == h->launch_cache.end()) {
+        if (h->launch_cache.size() > 4096) h->launch_cache.clear();
+        it = h->launch_cache.emplace(std::move(key), build_launch(h, a, three_pass)).first;
     }
+    const TcLaunch &L = static_cast<const TcLaunch &>(*it->second);
+    ProfileScope prof(h, 0, L.flops);
+    L.v.kernel<<<L.grid, L.threads, L.v.smem, h->stream>>>(L.p);
+    try {
+        check_launch("gemm_tf32_tcgen05_kernel");
+    } catch (const Error &err) {
+        throw Error(err.code, std::string(err.what()) + L.desc);    // an asynchronous fault is otherwise hard to place
+    }
+    count_launch(h);
+    prof.finish();
 }
 
 }  // namespace nb

@@ -5,6 +5,9 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <algorithm>
+#include <map>
+#include <memory>
 #include <stdexcept>
 #include <string>
 #include <unordered_map>
@@ -42,6 +45,15 @@ typedef CUresult (*nb_encode_tiled_fn)(CUtensorMap *, CUtensorMapDataType, cuuin
                                        CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
                                        CUtensorMapFloatOOBfill);
 
+typedef CUresult (*nb_get_address_range_fn)(CUdeviceptr *, size_t *, CUdeviceptr);
+
+namespace nb {
+struct Arena;
+// A launch whose parameters (tile geometry, tensor maps, grid) were worked out before: kept per handle under a key
+// made of every argument that went into them, so that a layer's second and later forward passes only launch.
+struct LaunchRecord { virtual ~LaunchRecord() {} };
+}  // namespace nb
+
 struct nb_handle_s {
     int device = 0;
     cudaStream_t stream = 0;
@@ -51,38 +63,80 @@ struct nb_handle_s {
     std::string last_error;
     int *d_status = nullptr;            // device status word (nb::DEV_*)
     nb_encode_tiled_fn encode_tiled = nullptr;
+    nb_get_address_range_fn get_address_range = nullptr;   // cuMemGetAddressRange: the allocation a pointer lies in
     unsigned long long launches = 0;
     // optional per-launch event timing of the contraction kernels
     struct Timed { cudaEvent_t start, stop; double flops; int kind; };
     bool profiling = false;
     std::vector<Timed> timed;
     std::vector<cudaEvent_t> event_pool;    // events are re-used across profiling windows
-    // encoded TMA descriptors, keyed by every argument of the encode call (layers keep their buffers, so a
-    // network's forward pass re-uses the same few dozen maps on every call)
-    std::unordered_map<std::string, CUtensorMap> tensor_maps;
+    std::unordered_map<std::string, std::unique_ptr<nb::LaunchRecord>> launch_cache;
+    std::shared_ptr<nb::Arena> arena;
+    // device allocations seen by check_extent: [base, end) by base address
+    std::map<uintptr_t, uintptr_t> known_ranges;
 };
 
 namespace nb {
 
 // ------------------------------------------------------------ device memory
+// Every device buffer of the library comes out of a per-handle arena: a few large cudaMalloc'd chunks, carved first-fit.
+// Why not one cudaMalloc per buffer: a TMA tiled load whose box lies partly (or wholly) at out-of-bounds coordinates
+// delivers the fill value for those elements but still READS the addresses the coordinates map to (measured: the L2
+// read-sector count of a box load does not depend on how much of the box is in bounds).  The zero padding of a
+// convolution is made of exactly such loads, so they read the row above a tensor's first image, below its last
+// one, and the rows past a weight matrix's last filter.  Those addresses must be mapped.  Inside a chunk they
+// are: a buffer's neighbours are other buffers of the library, and END_GUARD bytes at both ends of every chunk
+// are never handed out.  Launches check the range they can reach against the chunk (check_extent).
+struct Arena {
+    static constexpr size_t END_GUARD = (size_t)16 << 20;
+    static constexpr size_t MIN_CHUNK = (size_t)256 << 20;
+    struct Chunk {
+        char *base = nullptr;
+        size_t size = 0;
+        std::map<size_t, size_t> free;      // offset -> length of the free runs
+    };
+    std::vector<Chunk> chunks;
+    std::unordered_map<void *, std::pair<char *, size_t>> live;     // pointer -> (its chunk's base, length)
+    size_t in_use = 0;
+    ~Arena();
+    void *alloc(size_t bytes);
+    void release(void *p);
+    // the arena of the handle whose call is running on this thread (set by the C-ABI entry points)
+    static std::shared_ptr<Arena> &current();
+};
+
 struct DeviceBuffer {
     float *p = nullptr;
     size_t n = 0;
+    size_t guard = 0;                       // floats after the n-th that belong to the buffer too (never read back)
+    std::shared_ptr<Arena> owner;
     DeviceBuffer() {}
     DeviceBuffer(const DeviceBuffer &) = delete;
     DeviceBuffer &operator=(const DeviceBuffer &) = delete;
     ~DeviceBuffer() { release(); }
-    void alloc(size_t count) {
+    // guard_floats: extra floats behind the tensor that TMA boxes running past its last row may read
+    void alloc(size_t count, size_t guard_floats = 0) {
         release();
-        // 256 bytes of tail slack: a TMA box whose rows do not start on 128-byte lines may touch the line after the
-        // tensor's last element
-        if (count) NB_CHECK_CUDA(cudaMalloc((void **)&p, count * sizeof(float) + 256));
+        if (count) {
+            owner = Arena::current();
+            if (!owner) throw Error(NB_ERR_INVALID_ARG, "device allocation outside a library call");
+            p = (float *)owner->alloc((count + guard_floats) * sizeof(float));
+        }
         n = count;
+        guard = guard_floats;
+    }
+    // true when the buffer had to grow (the caller may want to know that an allocation happened)
+    bool reserve(size_t count, size_t guard_floats = 0) {
+        if (n >= count && guard >= guard_floats) return false;
+        alloc(count, guard_floats);
+        return true;
     }
     void release() {
-        if (p) cudaFree(p);
+        if (p && owner) owner->release(p);
         p = nullptr;
         n = 0;
+        guard = 0;
+        owner.reset();
     }
 };
 
@@ -124,6 +178,7 @@ struct GemmArgs {
     const float *shift = nullptr;   // may be null (=0)
     const float *addend = nullptr;  // may be null; same indexing as y unless res_stride > 0
     long ld_addend = 0;
+    bool addend_after_act = false;  // y = act(acc*scale + shift) + addend instead of act(acc*scale + shift + addend)
     // residual form of the addend (tensor-core conv kernels): NHWC tensor [batch][res_h][res_w][ld_addend] of
     // which output pixel (n,oh,ow) takes channels [0,res_c) of pixel (n, oh*res_stride, ow*res_stride)
     int res_stride = 0, res_c = 0, res_h = 0, res_w = 0;
@@ -182,6 +237,9 @@ void launch_weight_rowwin(nb_handle_s *h, const float *w, float *dst, int F, int
 // NCHW or NHWC [N][C][H][W] -> [N][H][Wp][4] with `pad` zero pixels on the left, zeros on the right and in channels >= C
 void launch_rowwin_input(nb_handle_s *h, const float *x, float *dst, int N, int C, int H, int W, int Wp, int pad, bool nhwc_in,
                          bool round);
+// decoded 8-bit images [N][H][W][C] -> fp32 NCHW batch, or (rowwin) the first convolution's [N][H][Wp][4] tensor
+void launch_u8_pack(nb_handle_s *h, const unsigned char *img, float *dst, int N, int C, int H, int W, bool rowwin, int Wp,
+                    int pad, bool round);
 void launch_weight_relayout(nb_handle_s *h, const float *w_oihw, float *dst, int F, int C, int k, int Cp);
 // weights OIHW -> [F][Kpad] with column (kh,kw,c), zero padded: the B operand of the gathered-A convolution
 void launch_weight_pack(nb_handle_s *h, const float *w_oihw, float *dst, int F, int C, int k, int Kpad);
@@ -207,17 +265,25 @@ struct ProfileScope {
     ProfileScope(nb_handle_s *hh, int kind, double flops) : h(hh), on(hh->profiling) {
         if (!on) return;
         t.kind = kind; t.flops = flops;
+        t.start = t.stop = nullptr;
         auto take = [&](cudaEvent_t &e) {
-            if (h->event_pool.empty()) cudaEventCreate(&e);
+            if (h->event_pool.empty()) NB_CHECK_CUDA(cudaEventCreate(&e));
             else { e = h->event_pool.back(); h->event_pool.pop_back(); }
         };
         take(t.start); take(t.stop);
-        cudaEventRecord(t.start, h->stream);
+        NB_CHECK_CUDA(cudaEventRecord(t.start, h->stream));
+    }
+    // call after the launch; a scope that is abandoned (the launch threw) returns its events to the pool
+    void finish() {
+        if (!on) return;
+        on = false;
+        NB_CHECK_CUDA(cudaEventRecord(t.stop, h->stream));
+        h->timed.push_back(t);
     }
     ~ProfileScope() {
         if (!on) return;
-        cudaEventRecord(t.stop, h->stream);
-        h->timed.push_back(t);
+        if (t.start) h->event_pool.push_back(t.start);
+        if (t.stop) h->event_pool.push_back(t.stop);
     }
 };
 
@@ -227,5 +293,20 @@ void encode_tensor_map(nb_handle_s *h, CUtensorMap *tm, const void *base, int ra
 
 inline void count_launch(nb_handle_s *h, int n = 1) { h->launches += (unsigned long long)n; }
 void check_launch(const char *what);
+
+// Fails with NB_ERR_INVALID_ARG when [p + lo_bytes, p + hi_bytes) is not inside ONE device allocation (as the driver
+// reports it for p).  Pointers the driver does not know as an allocation (module globals, host memory) pass.
+void check_extent(nb_handle_s *h, const void *p, long long lo_bytes, long long hi_bytes, const char *what);
+
+// Appends the raw bytes of a value to a cache key.
+template <class T>
+inline void key_add(std::string &k, const T &v) { k.append(reinterpret_cast<const char *>(&v), sizeof v); }
+// Every field of a GemmArgs that decides a launch's parameters.
+std::string gemm_args_key(const GemmArgs &a, char tag, int extra);
+
+// Per-device set-up of the tensor-core kernels (shared-memory limits; also loads their code), once per handle.
+void gemm_tc_prepare_device();
+void conv_halo_prepare_device();
+void elementwise_prepare_device();
 
 }  // namespace nb

@@ -205,7 +205,30 @@ void nb_network_s::build(const std::string &cfg_text, int batch_override) {
             l->activation = d.activation;
             l->weight_floats = l->lstm->weight_count();
         } else if (s.name == "rnn") {
-            throw Error(NB_ERR_UNSUPPORTED, "[rnn] layers are not implemented");
+            nb_rnn_desc_t d{};
+            d.time_steps = time_steps; d.batch = batch; d.inputs = (int)flat; d.hidden = 0;
+            s.get("output", &d.hidden); s.get("batch_normalize", &d.batch_normalize);
+            d.activation = section_activation(s, "rnn");
+            l->type = LT_RNN;
+            l->rnn.reset(new RnnPlan(h, d));
+            l->C = d.hidden; l->H = l->W = 1;
+            l->activation = d.activation;
+            l->weight_floats = l->rnn->weight_count();
+        } else if (s.name == "rbm") {
+            // inference through a pre-trained RBM is a connected layer on the hidden bias
+            // (rbm_layer_t::forward, rbm_layer.cc:345-374; weight file: hidden_bias, weight, rbm_layer.cc:150-157)
+            nb_fc_desc_t d{};
+            d.batch = rows; d.inputs = (int)flat; d.outputs = 0;
+            s.get("output", &d.outputs);
+            d.activation = section_activation(s, "rbm");
+            l->type = LT_RBM;
+            l->fc.reset(new FcPlan(h, d));
+            if (!layers.empty() && layers.back()->nhwc && H * W > 1) {
+                l->fc->perm_c = C; l->fc->perm_h = H; l->fc->perm_w = W;
+            }
+            l->C = d.outputs; l->H = l->W = 1;
+            l->activation = d.activation;
+            l->weight_floats = (size_t)d.outputs + (size_t)d.outputs * flat;
         } else {
             throw Error(NB_ERR_CONFIG, "unknown layer type " + s.name);
         }
@@ -226,7 +249,6 @@ void nb_network_s::build(const std::string &cfg_text, int batch_override) {
         layers.push_back(std::move(l));
     }
     if (layers.empty()) throw Error(NB_ERR_CONFIG, "network has no layers");
-    input_dev.alloc(input_size * rows);
 }
 
 void nb_network_s::load_weights(const float *stream, size_t count, int mem) {
@@ -246,7 +268,7 @@ void nb_network_s::load_weights(const float *stream, size_t count, int mem) {
             l.conv->set_weights(p + F, p, d.batch_normalize ? p + F + wn : nullptr,
                                 d.batch_normalize ? p + 2 * F + wn : nullptr, d.batch_normalize ? p + 3 * F + wn : nullptr,
                                 mem);
-        } else if (l.type == LT_CONNECTED) {
+        } else if (l.type == LT_CONNECTED || l.type == LT_RBM) {
             const nb_fc_desc_t &d = l.fc->d;
             const size_t O = d.outputs, wn = O * d.inputs;
             l.fc->set_weights(p + O, p, d.batch_normalize ? p + O + wn : nullptr,
@@ -254,15 +276,56 @@ void nb_network_s::load_weights(const float *stream, size_t count, int mem) {
                               mem);
         } else if (l.type == LT_LSTM) {
             l.lstm->set_weights(p, l.weight_floats, mem);
+        } else if (l.type == LT_RNN) {
+            l.rnn->set_weights(p, l.weight_floats, mem);
         }
         pos += l.weight_floats;
     }
     weights_loaded = true;
+    prepared_mode = -1;
+    prepare();
 }
 
-void nb_network_s::forward(const float *input) {
-    if (!weights_loaded && weight_count() > 0) throw Error(NB_ERR_NO_WEIGHTS, "network forward before weights were loaded");
-    NB_REQUIRE(input != nullptr, "null input pointer");
+nb_network_s::~nb_network_s() {
+    drop_graphs();
+    for (Slot &sl : slot) {
+        if (sl.u8) (void)cudaFree(sl.u8);
+        if (sl.copied) (void)cudaEventDestroy(sl.copied);
+        if (sl.done) (void)cudaEventDestroy(sl.done);
+    }
+    if (copy_stream) (void)cudaStreamDestroy(copy_stream);
+    if (capture_stream) (void)cudaStreamDestroy(capture_stream);
+}
+
+size_t nb_network_s::workspace_bytes() const {
+    size_t n = (input_nhwc.n + convert_tmp.n + slot[0].f32.n + slot[1].f32.n) * sizeof(float);
+    for (auto &lp : layers) {
+        if (lp->conv) n += lp->conv->workspace_bytes();
+        if (lp->fc) n += lp->fc->workspace_bytes();
+        if (lp->lstm) n += lp->lstm->workspace_bytes();
+        if (lp->rnn) n += lp->rnn->workspace_bytes();
+    }
+    return n;
+}
+
+void nb_network_s::prepare() {
+    if (prepared_mode == h->math_mode && prepared_fuse == fuse) return;
+    drop_graphs();
+    walk(nullptr, IN_F32, true);
+    NB_CHECK_CUDA(cudaStreamSynchronize(h->stream));
+    prepared_mode = h->math_mode;
+    prepared_fuse = fuse;
+}
+
+bool nb_network_s::first_layer_takes_rowwin() const {
+    if (layers.empty() || layers[0]->type != LT_CONVOLUTIONAL) return false;
+    const ConvPlan &c = *layers[0]->conv;
+    return c.rowwin_ok && h->math_mode != NB_MATH_FP32 && c.path(ForwardOpts()) == PATH_SIMT;
+}
+
+// One pass over the layer list.  dry: nothing is launched; every layer sizes and allocates the scratch this pass
+// would use, so that real passes allocate nothing.
+void nb_network_s::walk(const float *input, int kind, bool dry) {
     const bool tf32 = h->math_mode == NB_MATH_TF32;
     const int n = (int)layers.size();
 
@@ -274,8 +337,8 @@ void nb_network_s::forward(const float *input) {
         if (j >= n) return false;
         NetLayer &c = *layers[j];
         if (c.type == LT_CONVOLUTIONAL) return c.conv->path(ForwardOpts()) == PATH_TC;
-        if (c.type == LT_CONNECTED) return c.fc->path() == PATH_TC;
-        if (c.type == LT_LSTM) return true;
+        if (c.type == LT_CONNECTED || c.type == LT_RBM) return c.fc->path() == PATH_TC;
+        if (c.type == LT_LSTM || c.type == LT_RNN) return true;
         return false;
     };
 
@@ -289,6 +352,7 @@ void nb_network_s::forward(const float *input) {
             case LT_CONVOLUTIONAL: {
                 ForwardOpts o;
                 o.x_nhwc = cur_nhwc; o.y_nhwc = true; o.x_rounded = cur_rounded; o.round_out = round_out;
+                if (i == 0 && kind == IN_ROWWIN) o.x_rowwin = true;
                 l.materialised = true;
                 // conv -> maxpool 2x2/2: the pooled tensor is produced by the conv epilogue
                 bool referenced = false;        // a later shortcut reads this layer's own output
@@ -300,7 +364,8 @@ void nb_network_s::forward(const float *input) {
                         const bool pool_round = consumer_is_tf32(i + 1);
                         o.round_out = pool_round;
                         o.pool_out = pl.out_ptr;
-                        l.conv->forward(cur, nullptr, o);
+                        if (dry) l.conv->reserve(o);
+                        else l.conv->forward(cur, nullptr, o);
                         l.materialised = false;
                         pl.out_is_rounded = pool_round;
                         cur = pl.out_ptr; cur_nhwc = true; cur_rounded = pool_round; cur_round = nullptr;
@@ -319,7 +384,8 @@ void nb_network_s::forward(const float *input) {
                         o.residual = cl.out_ptr;
                         o.res_c = sd.conn_channels; o.res_h = sd.conn_height; o.res_w = sd.conn_width;
                         o.res_act = sd.activation;
-                        l.conv->forward(cur, sl.out_ptr, o);
+                        if (dry) l.conv->reserve(o);
+                        else l.conv->forward(cur, sl.out_ptr, o);
                         l.materialised = false;
                         sl.out_is_rounded = sc_round;
                         cur = sl.out_ptr; cur_nhwc = true; cur_rounded = sc_round; cur_round = nullptr;
@@ -327,16 +393,20 @@ void nb_network_s::forward(const float *input) {
                         continue;
                     }
                 }
-                l.conv->forward(cur, l.out_ptr, o);
+                if (dry) l.conv->reserve(o);
+                else l.conv->forward(cur, l.out_ptr, o);
                 break;
             }
-            case LT_CONNECTED: {
+            case LT_CONNECTED:
+            case LT_RBM: {
                 ForwardOpts o;
                 o.round_out = round_out;
                 const float *x = cur;
                 o.x_rounded = cur_rounded;
+                o.x_foreign = i == 0;
                 if (tf32 && cur_round) { x = cur_round; o.x_rounded = true; }
-                l.fc->forward(x, l.out_ptr, o, rows);
+                if (dry) l.fc->reserve(o, rows);
+                else l.fc->forward(x, l.out_ptr, o, rows);
                 break;
             }
             case LT_MAXPOOL:
@@ -345,28 +415,34 @@ void nb_network_s::forward(const float *input) {
                 d.layout = cur_nhwc ? NB_LAYOUT_NHWC : NB_LAYOUT_NCHW;
                 if (!cur_nhwc) {
                     // only possible for the first layer: bring the NCHW input to NHWC first
-                    if (input_nhwc.n < input_size * rows) input_nhwc.alloc(input_size * rows);
-                    launch_layout(h, cur, input_nhwc.p, rows, in_c, in_h, in_w, true, false);
+                    input_nhwc.reserve(input_size * rows);
+                    if (!dry) launch_layout(h, cur, input_nhwc.p, rows, in_c, in_h, in_w, true, false);
                     cur = input_nhwc.p;
                     d.layout = NB_LAYOUT_NHWC;
                 }
-                launch_pool(h, d, cur, l.out_ptr, round_out);
+                if (!dry) launch_pool(h, d, cur, l.out_ptr, round_out);
                 break;
             }
             case LT_SHORTCUT: {
-                launch_shortcut(h, l.shortcut, cur, layers[l.conn]->out_ptr, l.out_ptr, round_out);
+                if (!dry) launch_shortcut(h, l.shortcut, cur, layers[l.conn]->out_ptr, l.out_ptr, round_out);
                 break;
             }
             case LT_DROPOUT: break;
             case LT_SOFTMAX: {
-                launch_softmax(h, cur, l.out_ptr, rows, l.C);
+                if (!dry) launch_softmax(h, cur, l.out_ptr, rows, l.C);
                 break;
             }
             case LT_LSTM: {
                 const float *x = cur;
                 bool xr = cur_rounded;
                 if (tf32 && cur_round) { x = cur_round; xr = true; }
-                l.lstm->forward(x, l.out_ptr, nullptr, xr, l.out_round_ptr);
+                if (dry) l.lstm->reserve(true, xr, true, i == 0);
+                else l.lstm->forward(x, l.out_ptr, nullptr, xr, l.out_round_ptr, i == 0);
+                break;
+            }
+            case LT_RNN: {
+                if (dry) l.rnn->reserve(cur_rounded, i == 0);
+                else l.rnn->forward(cur, l.out_ptr, cur_rounded, round_out, i == 0);
                 break;
             }
             default: throw Error(NB_ERR_UNSUPPORTED, "layer type not executable");
@@ -381,7 +457,120 @@ void nb_network_s::forward(const float *input) {
     }
 }
 
-void nb_network_s::layer_output(int index, float *dst, int mem) {
+void nb_network_s::drop_graphs() {
+    for (Graph &g : graphs) (void)cudaGraphExecDestroy(g.exec);
+    graphs.clear();
+    seen_inputs.clear();
+}
+
+// A pass, eagerly or as a graph replay.  A pass is captured the second time it is asked for with the same input
+// pointer: by then every launch of it has run once, so the capture itself makes no driver query and no allocation.
+void nb_network_s::run(const float *input, int kind) {
+    if (!weights_loaded && weight_count() > 0) throw Error(NB_ERR_NO_WEIGHTS, "network forward before weights were loaded");
+    NB_REQUIRE(input != nullptr, "null input pointer");
+    prepare();
+    static const bool sync_launches = [] {
+        const char *v = std::getenv("NEBULA_B200_SYNC_LAUNCHES");
+        return v && *v && *v != '0';
+    }();
+    if (!use_graph || h->profiling || sync_launches) { walk(input, kind, false); return; }
+    for (Graph &g : graphs)
+        if (g.input == input && g.kind == kind && g.mode == h->math_mode && g.fuse == fuse) {
+            NB_CHECK_CUDA(cudaGraphLaunch(g.exec, h->stream));
+            h->launches += g.launches;
+            return;
+        }
+    if (std::find(seen_inputs.begin(), seen_inputs.end(), (const void *)input) == seen_inputs.end()) {
+        if (seen_inputs.size() > 16) seen_inputs.clear();
+        seen_inputs.push_back(input);
+        walk(input, kind, false);
+        return;
+    }
+    if (!capture_stream) NB_CHECK_CUDA(cudaStreamCreateWithFlags(&capture_stream, cudaStreamNonBlocking));
+    cudaStream_t user = h->stream;
+    const unsigned long long before = h->launches;
+    cudaGraph_t graph = nullptr;
+    h->stream = capture_stream;
+    try {
+        NB_CHECK_CUDA(cudaStreamBeginCapture(capture_stream, cudaStreamCaptureModeThreadLocal));
+        walk(input, kind, false);
+        NB_CHECK_CUDA(cudaStreamEndCapture(capture_stream, &graph));
+    } catch (...) {
+        h->stream = user;
+        if (!graph) (void)cudaStreamEndCapture(capture_stream, &graph);
+        if (graph) (void)cudaGraphDestroy(graph);
+        throw;
+    }
+    h->stream = user;
+    Graph g{input, kind, h->math_mode, fuse, nullptr, h->launches - before};
+    h->launches = before;
+    cudaError_t e = cudaGraphInstantiate(&g.exec, graph, 0);
+    (void)cudaGraphDestroy(graph);
+    NB_CHECK_CUDA(e);
+    if (graphs.size() >= 8) { (void)cudaGraphExecDestroy(graphs.front().exec); graphs.erase(graphs.begin()); }
+    graphs.push_back(g);
+    NB_CHECK_CUDA(cudaGraphLaunch(g.exec, h->stream));
+    h->launches += g.launches;
+}
+
+void nb_network_s::forward_u8(const unsigned char *images_dev) {
+    NB_REQUIRE(images_dev != nullptr, "null image pointer");
+    if (recurrent) throw Error(NB_ERR_UNSUPPORTED, "8-bit image input for a recurrent network");
+    NB_REQUIRE(in_c == 3 || in_c == 1, "8-bit images need 1 or 3 channels (models/networks/convolutional.cc:305-311)");
+    prepare();
+    if (first_layer_takes_rowwin()) {
+        ConvPlan &c = *layers[0]->conv;
+        float *xw = c.x_rowwin.p;
+        launch_u8_pack(h, images_dev, xw, rows, in_c, in_h, in_w, true, c.rw_wp, c.d.padding, h->math_mode == NB_MATH_TF32);
+        run(xw, IN_ROWWIN);
+    } else {
+        slot[0].f32.reserve(input_size * rows);
+        launch_u8_pack(h, images_dev, slot[0].f32.p, rows, in_c, in_h, in_w, false, 0, 0, false);
+        run(slot[0].f32.p, IN_F32);
+    }
+}
+
+void nb_network_s::submit(const void *input_host, bool u8, float *output_host) {
+    NB_REQUIRE(input_host && output_host, "null host buffer");
+    if (u8 && recurrent) throw Error(NB_ERR_UNSUPPORTED, "8-bit image input for a recurrent network");
+    prepare();
+    if (!copy_stream) NB_CHECK_CUDA(cudaStreamCreateWithFlags(&copy_stream, cudaStreamNonBlocking));
+    Slot &s = slot[next_slot];
+    next_slot ^= 1;
+    if (!s.copied) {
+        NB_CHECK_CUDA(cudaEventCreateWithFlags(&s.copied, cudaEventDisableTiming));
+        NB_CHECK_CUDA(cudaEventCreateWithFlags(&s.done, cudaEventDisableTiming));
+    }
+    if (s.busy) {       // the submission before last used this slot: its pass must be over before the buffer is refilled
+        NB_CHECK_CUDA(cudaEventSynchronize(s.done));
+        s.busy = false;
+    }
+    const size_t elems = input_size * rows;
+    if (u8) {
+        if (!s.u8) NB_CHECK_CUDA(cudaMalloc((void **)&s.u8, elems));
+        NB_CHECK_CUDA(cudaMemcpyAsync(s.u8, input_host, elems, cudaMemcpyHostToDevice, copy_stream));
+    } else {
+        s.f32.reserve(elems);
+        NB_CHECK_CUDA(cudaMemcpyAsync(s.f32.p, input_host, elems * sizeof(float), cudaMemcpyHostToDevice, copy_stream));
+    }
+    NB_CHECK_CUDA(cudaEventRecord(s.copied, copy_stream));
+    NB_CHECK_CUDA(cudaStreamWaitEvent(h->stream, s.copied, 0));
+    if (u8) forward_u8(s.u8);
+    else run(s.f32.p, IN_F32);
+    layer_output(-1, output_host, NB_MEM_HOST, false);
+    NB_CHECK_CUDA(cudaEventRecord(s.done, h->stream));
+    s.busy = true;
+}
+
+void nb_network_s::wait() {
+    for (Slot &s : slot)
+        if (s.busy) {
+            NB_CHECK_CUDA(cudaEventSynchronize(s.done));
+            s.busy = false;
+        }
+}
+
+void nb_network_s::layer_output(int index, float *dst, int mem, bool sync) {
     const int n = (int)layers.size();
     if (index < 0) index += n;
     NB_REQUIRE(index >= 0 && index < n, "layer index out of range");
@@ -397,11 +586,11 @@ void nb_network_s::layer_output(int index, float *dst, int mem) {
             launch_layout(h, src, dst, rows, l.C, l.H, l.W, false, false);
             return;
         }
-        if (convert_tmp.n < total) convert_tmp.alloc(total);
+        convert_tmp.reserve(total);
         launch_layout(h, src, convert_tmp.p, rows, l.C, l.H, l.W, false, false);
         src = convert_tmp.p;
     }
     NB_CHECK_CUDA(cudaMemcpyAsync(dst, src, total * sizeof(float),
                                   mem == NB_MEM_DEVICE ? cudaMemcpyDeviceToDevice : cudaMemcpyDeviceToHost, h->stream));
-    if (mem == NB_MEM_HOST) NB_CHECK_CUDA(cudaStreamSynchronize(h->stream));
+    if (mem == NB_MEM_HOST && sync) NB_CHECK_CUDA(cudaStreamSynchronize(h->stream));
 }

@@ -9,16 +9,16 @@
 
 namespace nb {
 
-void upload(nb_handle_s *h, DeviceBuffer &dst, const float *src, size_t n, int mem) {
-    dst.alloc(n);
+void upload(nb_handle_s *h, DeviceBuffer &dst, const float *src, size_t n, int mem, size_t guard) {
+    dst.alloc(n, guard);
     if (!n) return;
     NB_REQUIRE(src != nullptr, "null source pointer");
     NB_CHECK_CUDA(cudaMemcpyAsync(dst.p, src, n * sizeof(float),
                                   mem == NB_MEM_DEVICE ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, h->stream));
     if (mem == NB_MEM_HOST) NB_CHECK_CUDA(cudaStreamSynchronize(h->stream));   // the host buffer may go away
 }
-void upload_vec(nb_handle_s *h, DeviceBuffer &dst, const std::vector<float> &v) {
-    upload(h, dst, v.data(), v.size(), NB_MEM_HOST);
+void upload_vec(nb_handle_s *h, DeviceBuffer &dst, const std::vector<float> &v, size_t guard) {
+    upload(h, dst, v.data(), v.size(), NB_MEM_HOST, guard);
 }
 // Per-column epilogue vectors are read 32 columns at a time: pad them to a multiple of 32.
 void upload_padded(nb_handle_s *h, DeviceBuffer &dst, std::vector<float> v, float fill) {
@@ -84,18 +84,22 @@ void ConvPlan::set_weights(const float *weight, const float *bias, const float *
     const size_t wn = (size_t)d.filters * d.channels * d.size * d.size;
     DeviceBuffer raw;
     upload(h, raw, weight, wn, mem);
-    w.exact.alloc((size_t)d.size * d.size * d.filters * Cp);
+    w.exact.alloc((size_t)d.size * d.size * d.filters * Cp, weight_guard(Cp));
     w.split_ready = false;
     launch_weight_relayout(h, raw.p, w.exact.p, d.filters, d.channels, d.size, Cp);
+    const bool tensor_cores = h->encode_tiled && h->cc_major == 10;
+    if (tensor_cores) w.ensure_split(h);
     if (rowwin_ok) {
-        wr.exact.alloc((size_t)d.size * d.filters * rw_inner);
+        wr.exact.alloc((size_t)d.size * d.filters * rw_inner, weight_guard(rw_inner));
         wr.split_ready = false;
         launch_weight_rowwin(h, raw.p, wr.exact.p, d.filters, d.channels, d.size, rw_inner);
+        wr.ensure_split(h);
     }
     if (pack_ok) {
-        wp.exact.alloc((size_t)d.filters * Kpad);
+        wp.exact.alloc((size_t)d.filters * Kpad, weight_guard(Kpad));
         wp.split_ready = false;
         launch_weight_pack(h, raw.p, wp.exact.p, d.filters, d.channels, d.size, Kpad);
+        if (tensor_cores) wp.ensure_split(h);
     }
     NB_CHECK_CUDA(cudaStreamSynchronize(h->stream));
     std::vector<float> hb = to_host(h, bias, d.filters, mem), hg, hm, hv, sc, sh;
@@ -130,12 +134,30 @@ bool ConvPlan::can_fuse_shortcut(int conn_c, int conn_h, int conn_w) const {
            (conn_c % 4) == 0 && (d.filters % 4) == 0;
 }
 
+// Which of the three routes forward() takes, and the scratch each needs.
+size_t ConvPlan::reserve(const ForwardOpts &o) {
+    const GemmPath pth = path(o);
+    const size_t xin = (size_t)d.batch * d.channels * d.height * d.width;
+    const size_t yout = (size_t)d.batch * d.filters * OH * OW;
+    const bool tc_mode = h->math_mode != NB_MATH_FP32;
+    if (!o.y_nhwc) y_scratch.reserve(yout);
+    if (pth == PATH_SIMT && rowwin_ok && tc_mode) {
+        x_rowwin.reserve((size_t)d.batch * d.height * rw_wp * 4);
+    } else if (pth == PATH_SIMT && pack_ok && tc_mode && h->encode_tiled) {
+        // the kernel gathers x in place
+    } else if (pth != PATH_SIMT) {
+        const bool need_round = (pth == PATH_TC) && !o.x_rounded;
+        if (!o.x_nhwc || need_round || o.x_foreign) x_scratch.reserve(xin);
+    }
+    return workspace_bytes();
+}
+
 void ConvPlan::forward(const float *x, float *y, const ForwardOpts &o) {
     if (!ready) throw Error(NB_ERR_NO_WEIGHTS, "conv: forward before set_weights");
     NB_REQUIRE(x && (y || o.pool_out), "conv: null tensor pointer");
     const GemmPath pth = path(o);
     const size_t xin = (size_t)d.batch * d.channels * d.height * d.width;
-    const size_t yout = (size_t)d.batch * d.filters * OH * OW;
+    reserve(o);
 
     GemmArgs a;
     a.a_is_conv = true;
@@ -146,14 +168,9 @@ void ConvPlan::forward(const float *x, float *y, const ForwardOpts &o) {
     if (pth == PATH_SIMT && rowwin_ok && h->math_mode != NB_MATH_FP32) {
         // tensor-core route for 1-4 input channels: one TMA-fetched K slice per filter row
         const bool three = h->math_mode == NB_MATH_TF32X3;
-        // Slack before and after the tensor: the windows are 128 bytes long but start on 16-byte boundaries, the last
-        // one ends exactly at the tensor's end, and the copy engine was seen to touch memory past it (intermittent
-        // illegal-address faults when the buffer happened to end a mapping, none with 256 bytes of slack).
-        const size_t slack = (size_t)rw_wp * 4 + 64;            // one padded image row + 256 bytes, in floats
-        const size_t need = (size_t)d.batch * d.height * rw_wp * 4 + 2 * slack;
-        if (x_rowwin.n < need) x_rowwin.alloc(need);
-        float *xw = x_rowwin.p + slack;
-        launch_rowwin_input(h, x, xw, d.batch, d.channels, d.height, d.width, rw_wp, d.padding, o.x_nhwc, !three);
+        float *xw = x_rowwin.p;
+        if (o.x_rowwin) xw = const_cast<float *>(x);       // the caller already holds the input in this layout
+        else launch_rowwin_input(h, x, xw, d.batch, d.channels, d.height, d.width, rw_wp, d.padding, o.x_nhwc, !three);
         GemmArgs ra;
         ra.a = xw; ra.a_is_conv = true;
         ConvGeom &rg = ra.g;
@@ -166,12 +183,10 @@ void ConvPlan::forward(const float *x, float *y, const ForwardOpts &o) {
         float *yo = y;
         if (!o.y_nhwc) {
             NB_REQUIRE(o.addend == nullptr, "conv: addend needs NHWC output");
-            if (y_scratch.n < yout) y_scratch.alloc(yout);
             yo = y_scratch.p;
         }
         ra.y = yo; ra.ldy = d.filters;
         ra.algo_flops = 2.0 * (double)ra.M * d.filters * d.channels * d.size * d.size;
-        wr.ensure_split(h);
         ra.b = wr.hi.p; ra.b_lo = wr.lo.p;
         if (gemm_tc_supported(h, ra)) {
             gemm_tc(h, ra, three);
@@ -196,7 +211,6 @@ void ConvPlan::forward(const float *x, float *y, const ForwardOpts &o) {
         float *yo = y;
         if (!o.y_nhwc) {
             NB_REQUIRE(o.addend == nullptr, "conv: addend needs NHWC output");
-            if (y_scratch.n < yout) y_scratch.alloc(yout);
             yo = y_scratch.p;
         }
         pa.y = yo; pa.ldy = d.filters;
@@ -213,13 +227,14 @@ void ConvPlan::forward(const float *x, float *y, const ForwardOpts &o) {
     if (pth != PATH_SIMT) {
         const bool need_round = (pth == PATH_TC) && !o.x_rounded;
         if (!nhwc) {
-            if (x_scratch.n < xin) x_scratch.alloc(xin);
             launch_layout(h, x, x_scratch.p, d.batch, d.channels, d.height, d.width, true, need_round);
             xa = x_scratch.p;
             nhwc = true;
         } else if (need_round) {
-            if (x_scratch.n < xin) x_scratch.alloc(xin);
             launch_round_tf32(h, x, x_scratch.p, xin);
+            xa = x_scratch.p;
+        } else if (o.x_foreign) {
+            NB_CHECK_CUDA(cudaMemcpyAsync(x_scratch.p, x, xin * sizeof(float), cudaMemcpyDeviceToDevice, h->stream));
             xa = x_scratch.p;
         }
     }
@@ -242,7 +257,6 @@ void ConvPlan::forward(const float *x, float *y, const ForwardOpts &o) {
     float *yo = y;
     if (!o.y_nhwc) {
         NB_REQUIRE(o.addend == nullptr, "conv: addend needs NHWC output");
-        if (y_scratch.n < yout) y_scratch.alloc(yout);
         yo = y_scratch.p;
     }
     a.y = yo;
@@ -298,12 +312,13 @@ void FcPlan::set_weights(const float *weight, const float *bias, const float *g,
         NB_REQUIRE((size_t)perm_c * perm_h * perm_w == (size_t)d.inputs, "connected: permutation does not match inputs");
         DeviceBuffer raw;
         upload(h, raw, weight, wn, mem);
-        w.exact.alloc(wn);
+        w.exact.alloc(wn, weight_guard(d.inputs));
         launch_fc_permute(h, raw.p, w.exact.p, d.outputs, perm_c, perm_h, perm_w);
         NB_CHECK_CUDA(cudaStreamSynchronize(h->stream));
     } else {
-        upload(h, w.exact, weight, wn, mem);
+        upload(h, w.exact, weight, wn, mem, weight_guard(d.inputs));
     }
+    if (h->encode_tiled && h->cc_major == 10 && (d.inputs % 4) == 0 && d.inputs >= 32) w.ensure_split(h);
     std::vector<float> hb = to_host(h, bias, d.outputs, mem), hg, hm, hv, sc, sh;
     if (d.batch_normalize) {
         hg = to_host(h, g, d.outputs, mem);
@@ -324,42 +339,13 @@ GemmPath FcPlan::path() const {
     return h->math_mode == NB_MATH_TF32X3 ? PATH_TC3 : PATH_TC;
 }
 
-void FcPlan::forward(const float *x, float *y, const ForwardOpts &o, int rows) {
-    if (!ready) throw Error(NB_ERR_NO_WEIGHTS, "connected: forward before set_weights");
-    NB_REQUIRE(x && y, "connected: null tensor pointer");
-    const int M = rows > 0 ? rows : d.batch;
-    GemmPath pth = path();
-    if (pth != PATH_SIMT && (((uintptr_t)x) & 15)) pth = PATH_SIMT;
-    GemmArgs a;
-    const float *xa = x;
-    if (pth == PATH_TC && !o.x_rounded) {
-        const size_t n = (size_t)M * d.inputs;
-        if (x_scratch.n < n) x_scratch.alloc(n);
-        launch_round_tf32(h, x, x_scratch.p, n);
-        xa = x_scratch.p;
-    }
-    a.a = xa; a.lda = d.inputs;
-    a.ldb = d.inputs;
-    a.M = M; a.N = d.outputs; a.Kc = d.inputs;
-    a.scale = has_scale ? scale.p : nullptr;
-    a.shift = shift.p;
-    a.act = d.activation;
-    a.round_out_tf32 = o.round_out;
-    a.addend = o.addend; a.ld_addend = d.outputs;
-    a.y = y; a.ldy = d.outputs;
-    if (pth == PATH_SIMT) {
-        a.b = w.exact.p;
-        gemm_simt(h, a);
-        return;
-    }
-    w.ensure_split(h);
-    a.b = w.hi.p; a.b_lo = w.lo.p;
-    // Few rows and a long contraction (weight streaming): split K so that every SM pulls weights.
+// Few rows and a long contraction (weight streaming): split K so that every SM pulls weights.  Chosen from K, N
+// and the SM count only, never from the batch: a batch and its slices add in the same order.  Wide tiles keep the
+// most weight bytes in flight per SM; the split count then fills the SMs, and of the three tile widths the one
+// that leaves the fewest SMs idle in the last wave wins.
+void FcPlan::split_choice(bool tc, bool has_addend, int *S_out, int *block_n_out) const {
     int S = 1, block_n = 0;
-    if (pth == PATH_TC && !o.addend && (d.outputs % 4) == 0 && d.inputs >= 2048) {
-        // Chosen from K, N and the SM count only, never from the batch: a batch and its slices add in the same
-        // order.  Wide tiles keep the most weight bytes in flight per SM; the split count then fills the SMs, and
-        // of the three tile widths the one that leaves the fewest SMs idle in the last wave wins.
+    if (tc && !has_addend && (d.outputs % 4) == 0 && d.inputs >= 2048) {
         const int kblocks = (d.inputs + 31) / 32;
         double best = 0.0;
         for (int bn = 256; bn >= 64; bn /= 2) {
@@ -373,9 +359,54 @@ void FcPlan::forward(const float *x, float *y, const ForwardOpts &o, int rows) {
         }
         if (S == 1) block_n = 0;
     }
+    *S_out = S; *block_n_out = block_n;
+}
+
+size_t FcPlan::reserve(const ForwardOpts &o, int rows) {
+    const int M = rows > 0 ? rows : d.batch;
+    const GemmPath pth = path();
+    if ((pth == PATH_TC && !o.x_rounded) || (pth == PATH_TC3 && o.x_foreign)) x_scratch.reserve((size_t)M * d.inputs);
+    int S, bn;
+    split_choice(pth == PATH_TC, o.addend != nullptr, &S, &bn);
+    if (S > 1) split_ws.reserve((size_t)S * M * d.outputs);
+    return workspace_bytes();
+}
+
+void FcPlan::forward(const float *x, float *y, const ForwardOpts &o, int rows) {
+    if (!ready) throw Error(NB_ERR_NO_WEIGHTS, "connected: forward before set_weights");
+    NB_REQUIRE(x && y, "connected: null tensor pointer");
+    const int M = rows > 0 ? rows : d.batch;
+    GemmPath pth = path();
+    reserve(o, rows);
+    if (pth != PATH_SIMT && (((uintptr_t)x) & 15)) pth = PATH_SIMT;
+    GemmArgs a;
+    const float *xa = x;
+    if (pth == PATH_TC && !o.x_rounded) {
+        launch_round_tf32(h, x, x_scratch.p, (size_t)M * d.inputs);
+        xa = x_scratch.p;
+    } else if (pth == PATH_TC3 && o.x_foreign) {
+        NB_CHECK_CUDA(cudaMemcpyAsync(x_scratch.p, x, (size_t)M * d.inputs * sizeof(float), cudaMemcpyDeviceToDevice, h->stream));
+        xa = x_scratch.p;
+    }
+    a.a = xa; a.lda = d.inputs;
+    a.ldb = d.inputs;
+    a.M = M; a.N = d.outputs; a.Kc = d.inputs;
+    a.scale = has_scale ? scale.p : nullptr;
+    a.shift = shift.p;
+    a.act = d.activation;
+    a.round_out_tf32 = o.round_out;
+    a.addend = o.addend; a.ld_addend = d.outputs; a.addend_after_act = o.addend != nullptr && o.addend_post;
+    a.y = y; a.ldy = d.outputs;
+    if (pth == PATH_SIMT) {
+        a.b = w.exact.p;
+        gemm_simt(h, a);
+        return;
+    }
+    w.ensure_split(h);
+    a.b = w.hi.p; a.b_lo = w.lo.p;
+    int S, block_n;
+    split_choice(pth == PATH_TC, o.addend != nullptr, &S, &block_n);
     if (S > 1) {
-        const size_t need = (size_t)S * M * d.outputs;
-        if (split_ws.n < need) split_ws.alloc(need);
         GemmArgs sa = a;
         sa.split_k = S; sa.block_n_hint = block_n;
         sa.scale = nullptr; sa.shift = nullptr; sa.act = NB_ACT_LINEAR; sa.round_out_tf32 = false;
@@ -391,8 +422,7 @@ void FcPlan::forward(const float *x, float *y, const ForwardOpts &o, int rows) {
 // -------------------------------------------------------------------- lstm
 LstmPlan::LstmPlan(nb_handle_s *hh, const nb_lstm_desc_t &desc) : nb_plan_s(NB_PLAN_LSTM, hh), d(desc) {
     NB_REQUIRE(d.time_steps > 0 && d.batch > 0 && d.inputs > 0 && d.hidden > 0, "lstm: non-positive extent");
-    if (d.activation != NB_ACT_LINEAR)
-        throw Error(NB_ERR_UNSUPPORTED, "lstm: only activation=linear gate layers are supported");
+    NB_REQUIRE(d.activation > NB_ACT_UNDEFINED && d.activation < NB_ACT_COUNT, "lstm: undefined activation");
 }
 
 size_t LstmPlan::weight_count() const {
@@ -426,7 +456,8 @@ void LstmPlan::set_weights(const float *stream, size_t count, int mem) {
     }
     // gate rows in the order i, f, g(cell), o; file indices of those gates:
     const int file_of_gate[4] = {0, 1, 3, 2};
-    std::vector<float> u((size_t)4 * H * in), wr((size_t)4 * H * H), sh((size_t)4 * H, 0.0f);
+    const bool linear = d.activation == NB_ACT_LINEAR;
+    std::vector<float> u((size_t)4 * H * in), wr((size_t)4 * H * H), sh_u((size_t)4 * H, 0.0f), sh_w((size_t)4 * H, 0.0f);
     for (int gate = 0; gate < 4; gate++) {
         for (int side = 0; side < 2; side++) {      // 0: W (recurrent), 1: U (input)
             const Blob &b = blob[file_of_gate[gate] + (side ? 4 : 0)];
@@ -434,54 +465,74 @@ void LstmPlan::set_weights(const float *stream, size_t count, int mem) {
             std::vector<float> sc, s1;
             fold_bn(H, b.bias, b.g, b.m, b.v, d.batch_normalize != 0, sc, s1);
             // output row of hidden unit r, gate `gate`: 4*r + gate (a thread of the GEMM epilogue then holds all
-            // four gates of a unit in neighbouring columns)
+            // four gates of a unit in neighbouring columns); a batch-norm scale is folded into the weight row
             float *dst = side ? u.data() : wr.data();
             for (int r = 0; r < H; r++) {
                 const float s = sc.empty() ? 1.0f : sc[r];
                 const size_t row = (size_t)4 * r + gate;
                 for (size_t c = 0; c < gin; c++) dst[row * gin + c] = b.w[(size_t)r * gin + c] * s;
-                sh[row] += s1[r];
+                // linear gate layers: both sides' shifts are one vector, applied once by the input-side GEMM
+                ((side || linear) ? sh_u : sh_w)[row] += s1[r];
             }
         }
     }
-    upload_vec(h, wu.exact, u);
-    upload_vec(h, ww.exact, wr);
+    upload_vec(h, wu.exact, u, weight_guard(in));
+    upload_vec(h, ww.exact, wr, weight_guard(H));
     wu.split_ready = ww.split_ready = false;
-    upload_padded(h, shift, sh, 0.0f);
+    if (h->encode_tiled && h->cc_major == 10) {
+        if ((in % 4) == 0 && in >= 32) wu.ensure_split(h);
+        if ((H % 4) == 0 && H >= 32) ww.ensure_split(h);
+    }
+    upload_padded(h, shift, sh_u, 0.0f);
+    upload_padded(h, shift_w, sh_w, 0.0f);
+    NB_CHECK_CUDA(cudaStreamSynchronize(h->stream));
     ready = true;
 }
 
-void LstmPlan::forward(const float *x, float *out, float *cell, bool x_rounded, float *out_round) {
+size_t LstmPlan::reserve(bool own_cell, bool x_rounded, bool have_out_round, bool x_foreign) {
+    const int T = d.time_steps, B = d.batch, H = d.hidden, in = d.inputs;
+    const size_t rows = (size_t)T * B;
+    const bool tcm = h->math_mode != NB_MATH_FP32 && h->encode_tiled && h->cc_major == 10;
+    const bool tc_u = tcm && (in % 4) == 0 && in >= 32;
+    const bool tc_w = tcm && (H % 4) == 0 && H >= 32;
+    const bool three = h->math_mode == NB_MATH_TF32X3;
+    pre.reserve(rows * 4 * H);
+    if (!tc_w) z.reserve((size_t)B * 4 * H);
+    if (own_cell) cell_own.reserve(rows * H);
+    if (!have_out_round && tc_w && !three) h_round.reserve(rows * H);
+    if (tc_u && ((!three && !x_rounded) || (three && x_foreign))) x_round.reserve(rows * in);
+    if (d.activation != NB_ACT_LINEAR && h_zero.reserve((size_t)B * H))
+        NB_CHECK_CUDA(cudaMemsetAsync(h_zero.p, 0, (size_t)B * H * sizeof(float), h->stream));
+    return workspace_bytes();
+}
+
+void LstmPlan::forward(const float *x, float *out, float *cell, bool x_rounded, float *out_round, bool x_foreign) {
     if (!ready) throw Error(NB_ERR_NO_WEIGHTS, "lstm: forward before set_weights");
     NB_REQUIRE(x && out, "lstm: null tensor pointer");
     const int T = d.time_steps, B = d.batch, H = d.hidden, in = d.inputs;
     const size_t rows = (size_t)T * B;
-    const bool tc_u = h->math_mode != NB_MATH_FP32 && h->encode_tiled && h->cc_major == 10 && (in % 4) == 0 && in >= 32 &&
-                      !(((uintptr_t)x) & 15);
-    const bool tc_w = h->math_mode != NB_MATH_FP32 && h->encode_tiled && h->cc_major == 10 && (H % 4) == 0 && H >= 32;
+    const bool tcm = h->math_mode != NB_MATH_FP32 && h->encode_tiled && h->cc_major == 10;
+    const bool tc_u = tcm && (in % 4) == 0 && in >= 32 && !(((uintptr_t)x) & 15);
+    const bool tc_w = tcm && (H % 4) == 0 && H >= 32;
     const bool three = h->math_mode == NB_MATH_TF32X3;
-    if (pre.n < rows * 4 * H) pre.alloc(rows * 4 * H);
-    if (z.n < (size_t)B * 4 * H) z.alloc((size_t)B * 4 * H);
-    if (!cell) {
-        if (cell_own.n < rows * H) cell_own.alloc(rows * H);
-        cell = cell_own.p;
-    }
+    const bool linear = d.activation == NB_ACT_LINEAR;
+    reserve(cell == nullptr, x_rounded, out_round != nullptr, x_foreign);
+    if (!cell) cell = cell_own.p;
     float *hr = out_round;
-    if (!hr && tc_w && !three) {
-        if (h_round.n < rows * H) h_round.alloc(rows * H);
-        hr = h_round.p;
-    }
-    // 1. input-side projection of every time step in one GEMM: pre = X * U^T + (bU + bW)
+    if (!hr && tc_w && !three) hr = h_round.p;
+    // 1. input-side gate layers of every time step in one GEMM: pre = act(X * U^T + bU) (linear: + bW as well)
     {
         const float *xa = x;
         if (tc_u && !three && !x_rounded) {
-            if (x_round.n < rows * in) x_round.alloc(rows * in);
             launch_round_tf32(h, x, x_round.p, rows * in);
+            xa = x_round.p;
+        } else if (tc_u && three && x_foreign) {
+            NB_CHECK_CUDA(cudaMemcpyAsync(x_round.p, x, rows * in * sizeof(float), cudaMemcpyDeviceToDevice, h->stream));
             xa = x_round.p;
         }
         GemmArgs a;
         a.a = xa; a.lda = in; a.ldb = in; a.M = (int)rows; a.N = 4 * H; a.Kc = in;
-        a.shift = shift.p; a.act = NB_ACT_LINEAR; a.y = pre.p; a.ldy = 4 * H;
+        a.shift = shift.p; a.act = d.activation; a.y = pre.p; a.ldy = 4 * H;
         if (tc_u) {
             wu.ensure_split(h);
             a.b = wu.hi.p; a.b_lo = wu.lo.p;
@@ -491,20 +542,25 @@ void LstmPlan::forward(const float *x, float *out, float *cell, bool x_rounded, 
             gemm_simt(h, a);
         }
     }
-    // 2. the recurrence: z_t = pre_t + h_{t-1} * W^T, then the cell update
+    // 2. the recurrence: z_t = pre_t + act(h_{t-1} * W^T + bW), then the cell update.  With linear gate layers
+    //    step 0 has nothing to multiply (h_{-1} = 0 and bW is already in pre); otherwise act(bW) is not zero and
+    //    step 0 runs the recurrent layer on a zero state like every other step.
     for (int t = 0; t < T; t++) {
         const float *zt = pre.p + (size_t)t * B * 4 * H;
         float *ct = cell + (size_t)t * B * H, *ht = out + (size_t)t * B * H, *hrt = hr ? hr + (size_t)t * B * H : nullptr;
-        if (t > 0) {
+        const float *c_prev = t ? cell + (size_t)(t - 1) * B * H : nullptr;
+        if (t > 0 || !linear) {
             GemmArgs a;
-            const float *hprev = (tc_w && !three) ? hr + (size_t)(t - 1) * B * H : out + (size_t)(t - 1) * B * H;
+            const float *hprev = t == 0 ? h_zero.p
+                                        : ((tc_w && !three) ? hr + (size_t)(t - 1) * B * H : out + (size_t)(t - 1) * B * H);
             a.a = hprev; a.lda = H; a.ldb = H; a.M = B; a.N = 4 * H; a.Kc = H;
-            a.addend = zt; a.ld_addend = 4 * H; a.act = NB_ACT_LINEAR;
+            a.addend = zt; a.ld_addend = 4 * H; a.act = d.activation;
+            if (!linear) { a.shift = shift_w.p; a.addend_after_act = true; }
             if (tc_w) {
                 // the cell update runs in the GEMM epilogue: one launch per time step
                 ww.ensure_split(h);
                 a.b = ww.hi.p; a.b_lo = ww.lo.p;
-                a.lstm_H = H; a.lstm_c_prev = cell + (size_t)(t - 1) * B * H; a.lstm_c = ct; a.lstm_h = ht; a.lstm_h_round = hrt;
+                a.lstm_H = H; a.lstm_c_prev = c_prev; a.lstm_c = ct; a.lstm_h = ht; a.lstm_h_round = hrt;
                 gemm_tc(h, a, three);
                 continue;
             }
@@ -513,8 +569,92 @@ void LstmPlan::forward(const float *x, float *out, float *cell, bool x_rounded, 
             gemm_simt(h, a);
             zt = z.p;
         }
-        launch_lstm_cell(h, zt, t ? cell + (size_t)(t - 1) * B * H : nullptr, ct, ht, hrt, B, H);
+        launch_lstm_cell(h, zt, c_prev, ct, ht, hrt, B, H);
     }
+}
+
+// --------------------------------------------------------------------- rnn
+RnnPlan::RnnPlan(nb_handle_s *hh, const nb_rnn_desc_t &desc) : nb_plan_s(NB_PLAN_RNN, hh), d(desc) {
+    NB_REQUIRE(d.time_steps > 0 && d.batch > 0 && d.inputs > 0 && d.hidden > 0, "rnn: non-positive extent");
+    NB_REQUIRE(d.activation > NB_ACT_UNDEFINED && d.activation < NB_ACT_COUNT, "rnn: undefined activation");
+    // the three gates are connected layers built from the same section (rnn_layer.cc:47-54)
+    nb_fc_desc_t g{};
+    g.batch = d.batch; g.outputs = d.hidden; g.batch_normalize = d.batch_normalize; g.activation = d.activation;
+    g.inputs = d.inputs;
+    in_gate.reset(new FcPlan(h, g));
+    g.inputs = d.hidden;
+    hid_gate.reset(new FcPlan(h, g));
+    out_gate.reset(new FcPlan(h, g));
+}
+
+size_t RnnPlan::weight_count() const {
+    const size_t H = d.hidden, bn = d.batch_normalize ? 3 * H : 0;
+    return (H + H * d.inputs + bn) + 2 * (H + H * H + bn);
+}
+
+void RnnPlan::set_weights(const float *stream, size_t count, int mem) {
+    if (count != weight_count())
+        throw Error(NB_ERR_WEIGHTS, "rnn: weight stream has " + std::to_string(count) + " floats, layer needs " +
+                                        std::to_string(weight_count()));
+    // blobs in the order input gate, hidden gate, output gate (rnn_layer.cc:69-73), each a connected-layer blob
+    const size_t H = d.hidden;
+    size_t pos = 0;
+    FcPlan *gates[3] = {in_gate.get(), hid_gate.get(), out_gate.get()};
+    for (FcPlan *g : gates) {
+        const float *p = stream + pos;
+        const size_t wn = H * g->d.inputs;
+        g->set_weights(p + H, p, d.batch_normalize ? p + H + wn : nullptr, d.batch_normalize ? p + 2 * H + wn : nullptr,
+                       d.batch_normalize ? p + 3 * H + wn : nullptr, mem);
+        pos += H + wn + (d.batch_normalize ? 3 * H : 0);
+    }
+    ready = true;
+}
+
+size_t RnnPlan::reserve(bool x_rounded, bool x_foreign) {
+    const size_t T = d.time_steps, B = d.batch, H = d.hidden;
+    a_all.reserve(T * B * H);
+    state.reserve(T * B * H);
+    h0.reserve(B * H);
+    const bool tf32 = h->math_mode == NB_MATH_TF32;
+    ForwardOpts o;
+    o.x_rounded = x_rounded; o.x_foreign = x_foreign;
+    in_gate->reserve(o, (int)(T * B));
+    o.x_rounded = false; o.x_foreign = false;
+    hid_gate->reserve(o, (int)B);                   // step 0 reads the (unrounded) input-gate output
+    o.x_rounded = tf32;
+    out_gate->reserve(o, (int)((T > 1 ? T - 1 : 1) * B));
+    return workspace_bytes();
+}
+
+void RnnPlan::forward(const float *x, float *out, bool x_rounded, bool round_out, bool x_foreign) {
+    if (!ready) throw Error(NB_ERR_NO_WEIGHTS, "rnn: forward before set_weights");
+    NB_REQUIRE(x && out, "rnn: null tensor pointer");
+    const int T = d.time_steps, B = d.batch;
+    const size_t BH = (size_t)B * d.hidden;
+    const bool tf32 = h->math_mode == NB_MATH_TF32;     // stored states are then TF32 values, ready to be operands
+    reserve(x_rounded, x_foreign);
+    ForwardOpts o;
+    // a_t for every step at once: the input gate does not depend on the state
+    o.x_rounded = x_rounded; o.x_foreign = x_foreign;
+    in_gate->forward(x, a_all.p, o, T * B);
+    // step 0: the hidden gate reads the input gate's output, the output gate reads the hidden gate's
+    o = ForwardOpts();
+    o.round_out = tf32;
+    hid_gate->forward(a_all.p, h0.p, o, B);
+    o.addend = a_all.p; o.addend_post = true;
+    hid_gate->forward(a_all.p, state.p, o, B);          // s_0 = a_0 + h_0 (same product, then the sum)
+    // steps 1..T-1: h_t = hid(s_{t-1}), s_t = a_t + h_t
+    for (int t = 1; t < T; t++) {
+        ForwardOpts s;
+        s.x_rounded = tf32; s.round_out = tf32;
+        s.addend = a_all.p + t * BH; s.addend_post = true;
+        hid_gate->forward(state.p + (t - 1) * BH, state.p + t * BH, s, B);
+    }
+    // outputs: step 0 from h_0, the others from their states in one product
+    ForwardOpts q;
+    q.x_rounded = tf32; q.round_out = round_out;
+    out_gate->forward(h0.p, out, q, B);
+    if (T > 1) out_gate->forward(state.p + BH, out + BH, q, (T - 1) * B);
 }
 
 }  // namespace nb

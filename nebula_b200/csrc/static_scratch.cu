@@ -70,11 +70,17 @@ extern "C" int nb_fc_forward_static(nb_handle_t h, const float *x, const float *
         const bool three = h->math_mode == NB_MATH_TF32X3;
         // working copies: TF32 -> rounded x and rounded W; 3xTF32 -> hi and lo parts of W; plus the bias,
         // which the kernel reads 32 columns at a time (the copy is padded to a multiple of 64)
+        // Both operands are read by TMA from the array (never from the caller's tensors: a box that runs past a
+        // matrix's last row is delivered as zeros, but the load unit still reads the addresses behind the matrix,
+        // so those must lie inside the array as well).  Layout: bias | x | W (| W low part) | headroom, the headroom
+        // being the rows the widest weight tile can run past the last output: 256 * inputs + 32 floats.
         const size_t bn = round_up64((size_t)outputs);
-        const size_t need = !tensor_core ? 0 : bn + (three ? 2 * round_up64(wn) : round_up64(xn) + round_up64(wn));
+        const size_t headroom = 256 * (size_t)inputs + 32;
+        const size_t need = !tensor_core ? 0 : bn + round_up64(xn) + (three ? 2 : 1) * round_up64(wn) + headroom;
         if (need > NB_STATIC_SCRATCH_FLOATS)
             throw nb::Error(NB_ERR_INVALID_ARG,
-                            "connected (static): needs " + std::to_string(need) + " scratch floats, the built-in array holds " +
+                            "connected (static): needs " + std::to_string(need) + " scratch floats (operand copies plus " +
+                                std::to_string(headroom) + " of headroom), the built-in array holds " +
                                 std::to_string((size_t)NB_STATIC_SCRATCH_FLOATS) + " (16 MiB); use the plan-based nb_fc_forward");
         nb::GemmArgs a;
         a.lda = inputs; a.ldb = inputs;
@@ -91,9 +97,10 @@ extern "C" int nb_fc_forward_static(nb_handle_t h, const float *x, const float *
             a.shift = scratch;          // columns beyond `outputs` hold stale values that only masked lanes see
             scratch += bn;
             if (three) {
-                float *w_hi = scratch, *w_lo = scratch + round_up64(wn);
+                float *x_c = scratch, *w_hi = scratch + round_up64(xn), *w_lo = w_hi + round_up64(wn);
+                NB_CHECK_CUDA(cudaMemcpyAsync(x_c, x, xn * sizeof(float), cudaMemcpyDeviceToDevice, h->stream));
                 nb::launch_split_tf32(h, weight, w_hi, w_lo, wn);
-                a.a = x; a.b = w_hi; a.b_lo = w_lo;
+                a.a = x_c; a.b = w_hi; a.b_lo = w_lo;
             } else {
                 float *x_r = scratch, *w_r = scratch + round_up64(xn);
                 nb::launch_round_tf32(h, x, x_r, xn);

@@ -25,6 +25,7 @@ struct EpiParams {
     long ld_addend;
     int addend_vec;             // addend rows are 16-byte aligned
     int addend_cols;            // columns the addend covers (a residual may have fewer channels than the output)
+    int addend_post;            // add the addend AFTER the activation (the sum of two activated gate layers) instead of before
     // residual mode (res_stride > 0): the addend is an NHWC tensor [NB][res_h][res_w][ld_addend] and output
     // pixel (n,oh,ow) takes pixel (n, oh*res_stride, ow*res_stride) of it -- the reference's shortcut
     // (common/utils.cc:28-60) with sample == 1; otherwise the addend has the output's own row indexing
@@ -146,16 +147,22 @@ __device__ __forceinline__ void tma_store_wait_read() {
     asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
 }
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-// named barrier `id` over the 128 threads of one epilogue group
-__device__ __forceinline__ void epilogue_bar_sync(int id) { asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory"); }
+// Named barrier `id` over the 128 threads of one epilogue group.  The form without `.aligned` counts threads, not
+// warps, so a warp whose lanes arrive from different sides of a branch is still counted once per lane; the warp is
+// re-converged first because the instructions that follow (tcgen05.ld, the next barrier) want it whole.
+__device__ __forceinline__ void epilogue_bar_sync(int id) {
+    __syncwarp();
+    asm volatile("barrier.cta.sync %0, 128;" ::"r"(id) : "memory");
+}
 // AND-vote across the 128 threads of an epilogue group (named barrier `id`), so that leaving
 // the tile loop is a uniform decision and no thread is left alone at a later bar.sync.
 __device__ __forceinline__ bool epilogue_all(bool pred, int id) {
     uint32_t r;
+    __syncwarp();       // the waits before this vote end lane by lane
     asm volatile(
         "{\n\t.reg .pred p, q;\n\t"
         "setp.ne.b32 p, %1, 0;\n\t"
-        "bar.red.and.pred q, %2, 128, p;\n\t"
+        "barrier.cta.red.and.pred q, %2, 128, p;\n\t"
         "selp.b32 %0, 1, 0, q;\n\t}"
         : "=r"(r)
         : "r"((uint32_t)pred), "r"(id)
@@ -206,7 +213,9 @@ __device__ __forceinline__ void umma_commit(uint64_t *bar) {
                  : "memory");
 }
 
+// Warp-wide (.sync.aligned): the warp is re-converged first, whatever branch its lanes came from.
 __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&v)[32]) {
+    __syncwarp();
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -218,7 +227,10 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&v)[32])
         : "r"(taddr)
         : "memory");
 }
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld_wait() {
+    __syncwarp();
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
 
 
 // One 128-row x 32-column slab of accumulators (already in registers): folded batch-norm
@@ -250,7 +262,7 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams &e, const CUtenso
             v[j + 3] = __float_as_uint(__uint_as_float(v[j + 3]) + sh.w);
         }
     }
-    if (rw.arow && col0 < e.addend_cols) {
+    auto add_addend = [&]() {
         const float *arow = rw.arow + col0;
         if (col0 + 32 <= e.addend_cols && e.addend_vec) {
 #pragma unroll
@@ -266,6 +278,28 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams &e, const CUtenso
             for (int j = 0; j < 32; j++)
                 if (col0 + j < e.addend_cols) v[j] = __float_as_uint(__uint_as_float(v[j]) + arow[j]);
         }
+    };
+    auto activate = [&]() {
+        // the common ones inline, the rest through one out-of-line call per value
+        if (e.act == NB_ACT_RELU) {
+#pragma unroll
+            for (int j = 0; j < 32; j++) v[j] = __uint_as_float(v[j]) > 0.0f ? v[j] : 0u;
+        } else if (e.act == NB_ACT_LEAKY) {
+#pragma unroll
+            for (int j = 0; j < 32; j++) {
+                const float x = __uint_as_float(v[j]);
+                v[j] = __float_as_uint(x > 0.0f ? x : (float)(0.1 * (double)x));
+            }
+        } else if (e.act != NB_ACT_LINEAR) {
+#pragma unroll
+            for (int j = 0; j < 32; j++) v[j] = __float_as_uint(apply_activation_call(__uint_as_float(v[j]), e.act));
+        }
+    };
+    const bool has_addend = rw.arow && col0 < e.addend_cols;
+    if (has_addend && !e.addend_post) add_addend();
+    if (e.addend_post) {        // act(acc*scale + shift) + addend: two activated layers summed (lstm_layer.cc:252-282)
+        activate();
+        if (has_addend) add_addend();
     }
     if (e.lstm_H > 0) {
         // 32 columns = 8 hidden units x (i, f, g, o): the cell update of this row's units, with the CPU
@@ -315,20 +349,7 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams &e, const CUtenso
         }
         return;
     }
-    // activation: the common ones inline, the rest through one out-of-line call per value
-    if (e.act == NB_ACT_RELU) {
-#pragma unroll
-        for (int j = 0; j < 32; j++) v[j] = __uint_as_float(v[j]) > 0.0f ? v[j] : 0u;
-    } else if (e.act == NB_ACT_LEAKY) {
-#pragma unroll
-        for (int j = 0; j < 32; j++) {
-            const float x = __uint_as_float(v[j]);
-            v[j] = __float_as_uint(x > 0.0f ? x : (float)(0.1 * (double)x));
-        }
-    } else if (e.act != NB_ACT_LINEAR) {
-#pragma unroll
-        for (int j = 0; j < 32; j++) v[j] = __float_as_uint(apply_activation_call(__uint_as_float(v[j]), e.act));
-    }
+    if (!e.addend_post) activate();
     if (e.round_out) {
 #pragma unroll
         for (int j = 0; j < 32; j++) v[j] = __float_as_uint(round_tf32(__uint_as_float(v[j])));

@@ -215,6 +215,37 @@ class NetBuilder:
         self._push((output,))
         return self
 
+    def rnn(self, output, act="tanh", bn=False, bound=0.25):
+        """Three connected blobs in file order input, hidden, output gate (rnn_layer.cc:69-73)."""
+        inp = self._flat()
+        self.lines += ["[rnn]"] + (["batch_normalize=1"] if bn else []) + [f"output={output}", f"activation={act}", ""]
+        i = len(self.shapes)
+        for gname, gin in (("in", inp), ("hid", output), ("out", output)):
+            self.params.append(ParamSpec(f"l{i}.{gname}.bias", (output,), self.bias_init))
+            self.params.append(ParamSpec(f"l{i}.{gname}.weight", (output, gin), "uniform", gin, bound))
+            if bn:
+                self.params += [ParamSpec(f"l{i}.{gname}.scale", (output,), "bn_scale"),
+                                ParamSpec(f"l{i}.{gname}.mean", (output,), "bn_mean"),
+                                ParamSpec(f"l{i}.{gname}.var", (output,), "bn_var")]
+        f = 2.0 * (inp + 2 * output) * output * self.time_steps
+        self.flops += f
+        self.layer_flops.append(("rnn", f))
+        self._push((output,))
+        return self
+
+    def rbm(self, output, act="logistic"):
+        """Blob: hidden_bias, weight (rbm_layer.cc:150-157); forward is a connected layer (rbm_layer.cc:345-374)."""
+        inp = self._flat()
+        self.lines += ["[rbm]", f"output={output}", "k_step=1", f"activation={act}", ""]
+        i = len(self.shapes)
+        self.params.append(ParamSpec(f"l{i}.hidden_bias", (output,), self.bias_init))
+        self.params.append(ParamSpec(f"l{i}.weight", (output, inp), "he", inp))
+        f = 2.0 * inp * output
+        self.flops += f
+        self.layer_flops.append(("fc", f))
+        self._push((output,))
+        return self
+
     def build(self, input_dist="uniform01") -> Workload:
         return Workload(self.name, "\n".join(self.lines) + "\n", self.params, self.input_shape, input_dist,
                         self.recurrent, int(np.prod(self.shape)), self.flops, self.conv_flops,
@@ -273,6 +304,25 @@ def lstm2(batch=64, time_steps=128, input_size=1024, hidden=1024, classes=10000,
     return b.build("normal")
 
 
+def rnn2(batch=32, time_steps=16, input_size=256, hidden=256, classes=1000, layers=2, act="tanh", bn=False):
+    """Vanilla RNN layers and a projection, the shape of benchmarks/rnn_*/network.cfg."""
+    b = NetBuilder("rnn2", batch, input_size=input_size, time_steps=time_steps)
+    for _ in range(layers):
+        b.rnn(hidden, act, bn=bn, bound=1.0 / np.sqrt(hidden))
+    b.connected(classes, act="linear", init="uniform", bound=1.0 / np.sqrt(hidden))
+    return b.build("normal")
+
+
+def dbn(batch=32, height=128, width=128, channels=3, hidden=(2000, 1000, 500, 30), classes=62):
+    """Deep belief network at inference, the shape of benchmarks/dbn_large/network.cfg: [rbm] layers (logistic)
+    and a linear [connected] classifier."""
+    b = NetBuilder("dbn", batch, channels, height, width)
+    for h in hidden:
+        b.rbm(h, "logistic")
+    b.connected(classes, act="linear").softmax()
+    return b.build()
+
+
 def conv_micro(case="a", batch=64):
     """Single-convolution sweep, stride 1, fused bias + ReLU."""
     cin, cout, k, p, hw = {"a": (256, 256, 3, 1, 56), "b": (512, 512, 3, 1, 14), "c": (64, 256, 1, 0, 56)}[case]
@@ -281,6 +331,6 @@ def conv_micro(case="a", batch=64):
     return b.build("normal")
 
 
-WORKLOADS = {"alexnet": alexnet, "vgg16": vgg16, "resnet50": resnet50, "lstm2": lstm2,
+WORKLOADS = {"alexnet": alexnet, "vgg16": vgg16, "resnet50": resnet50, "lstm2": lstm2, "rnn2": rnn2, "dbn": dbn,
              "conv_a": lambda batch=64: conv_micro("a", batch), "conv_b": lambda batch=64: conv_micro("b", batch),
              "conv_c": lambda batch=64: conv_micro("c", batch)}

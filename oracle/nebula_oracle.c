@@ -321,3 +321,29 @@ void nbo_lstm_forward(const float *x, int T, int B, int in, int H, const nbo_fc_
     for (int g = 0; g < 4; g++) { free(gw[g]); free(gu[g]); }
     free(hid);
 }
+
+/* ------------------------------------------------------------------- RNN
+ * rnn_layer_t::forward (rnn_layer.cc:91-141).  Three connected layers built from
+ * one section: input gate (on x_t), hidden gate (on the state), output gate.
+ * state_t = in(x_t) + hid(.) by two saxpys onto a zeroed buffer (:107-115).  At
+ * step 0 the gates run forward() without an argument, i.e. on their predecessor's
+ * output (:100-101,116-117): the hidden gate reads the input gate's output and
+ * the output gate reads the hidden gate's output; from step 1 on both read the
+ * state.  blobs: input, hidden, output gate.  x [T,B,in], out [T,B,H]. */
+void nbo_rnn_forward(const float *x, int T, int B, int in, int H, const nbo_fc_blob *blobs /*3*/, int has_bn, int act,
+                     float *out) {
+    long n = (long)B * H;
+    float *a = (float *)malloc(sizeof(float) * n), *hd = (float *)malloc(sizeof(float) * n);
+    float *state = (float *)calloc(n, sizeof(float));
+    const nbo_fc_blob *bi = &blobs[0], *bh = &blobs[1], *bo = &blobs[2];
+    for (int t = 0; t < T; t++) {
+        nbo_connected_forward(x + (long)t * B * in, B, in, H, bi->w, bi->bias, has_bn ? bi->scale : NULL, bi->mean, bi->var, act, a);
+        nbo_connected_forward(t ? state : a, B, H, H, bh->w, bh->bias, has_bn ? bh->scale : NULL, bh->mean, bh->var, act, hd);
+        memset(state, 0, sizeof(float) * n);
+        for (long i = 0; i < n; i++) state[i] += 1.0f * a[i];
+        for (long i = 0; i < n; i++) state[i] += 1.0f * hd[i];
+        nbo_connected_forward(t ? state : hd, B, H, H, bo->w, bo->bias, has_bn ? bo->scale : NULL, bo->mean, bo->var, act,
+                              out + (long)t * n);
+    }
+    free(a); free(hd); free(state);
+}

@@ -136,6 +136,22 @@ def lstm_forward(x, blobs, H, act="linear", has_bn=False):
     return out, cell
 
 
+def rnn_forward(x, blobs, H, act, has_bn=False):
+    """x [T,B,in] time-major; blobs = 3 dicts in file order input, hidden, output gate.  Returns out [T,B,H]."""
+    x = _f32(x)
+    T, B, inp = x.shape
+    keep = []
+    arr = (_Blob * 3)()
+    for i, b in enumerate(blobs):
+        for name in ("bias", "w", "scale", "mean", "var"):
+            a = _f32(b[name]) if b.get(name) is not None else None
+            keep.append(a)
+            setattr(arr[i], name, _fp(a))
+    out = np.empty((T, B, H), np.float32)
+    lib().nbo_rnn_forward(_fp(x), T, B, inp, H, arr, int(has_bn), ACT[act], _fp(out))
+    return out
+
+
 # ------------------------------------------------------------------- configs
 @dataclass
 class Section:
@@ -227,6 +243,15 @@ def plan_network(text: str):
             out = (sec.get("output", 0),)
             layers.append(Layer("lstm", sec, out, dict(inp=_flat(prev), H=out[0], bn=sec.get("batch_normalize", 0),
                                                         act=sec.get("activation", None, str))))
+        elif sec.name == "rnn":
+            out = (sec.get("output", 0),)
+            layers.append(Layer("rnn", sec, out, dict(inp=_flat(prev), H=out[0], bn=sec.get("batch_normalize", 0),
+                                                       act=sec.get("activation", None, str))))
+        elif sec.name == "rbm":
+            # rbm_layer_t::forward is a connected layer on hidden_bias (rbm_layer.cc:345-374); no batch-norm
+            out = (sec.get("output", 0),)
+            layers.append(Layer("connected", sec, out, dict(inp=_flat(prev), out=out[0], bn=0,
+                                                             act=sec.get("activation", None, str))))
         else:
             raise ValueError(f"unknown layer type {sec.name}")
     return net, layers
@@ -243,6 +268,9 @@ def weight_count(layers) -> int:
         elif l.kind == "lstm":
             for g in range(8):
                 gin = p["H"] if g < 4 else p["inp"]
+                n += p["H"] + p["H"] * gin + (3 * p["H"] if p["bn"] else 0)
+        elif l.kind == "rnn":
+            for gin in (p["inp"], p["H"], p["H"]):
                 n += p["H"] + p["H"] * gin + (3 * p["H"] if p["bn"] else 0)
     return n
 
@@ -297,6 +325,9 @@ def forward_network(cfg_text: str, weights, x, batch=None, keep_all=False):
         elif l.kind == "lstm":
             blobs = [rd.fc(p["H"], p["H"] if g < 4 else p["inp"], p["bn"]) for g in range(8)]
             cur, _ = lstm_forward(cur, blobs, p["H"], p["act"], bool(p["bn"]))
+        elif l.kind == "rnn":
+            blobs = [rd.fc(p["H"], gin, p["bn"]) for gin in (p["inp"], p["H"], p["H"])]
+            cur = rnn_forward(cur, blobs, p["H"], p["act"], bool(p["bn"]))
         outs.append(cur)
     return outs if keep_all else outs[-1:]
 

@@ -43,6 +43,7 @@
 #include "dropout_layer.h"
 #include "lstm_layer.h"
 #include "pooling_layer.h"
+#include "rbm_layer.h"
 #include "rnn_layer.h"
 #include "shortcut_layer.h"
 #include "softmax_layer.h"
@@ -106,6 +107,7 @@ protected:
             else if (sec.name == "softmax") l = new nebula::softmax_layer_t(this, prev, nebula::SOFTMAX_LAYER);
             else if (sec.name == "lstm") l = new nebula::lstm_layer_t(this, prev, nebula::LSTM_LAYER);
             else if (sec.name == "rnn") l = new nebula::rnn_layer_t(this, prev, nebula::RNN_LAYER);
+            else if (sec.name == "rbm") l = new nebula::rbm_layer_t(this, prev, nebula::RBM_LAYER);
             else {
                 std::cerr << "ref_driver: unknown section " << sec.name << std::endl;
                 exit(2);
