@@ -2,6 +2,7 @@
 // dispatch into plans, kernels and the network executor.  Nothing here computes
 // on the host; a missing or non-sm_100 device is an error, not a fallback.
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <fstream>
 
@@ -25,7 +26,7 @@ int guarded(nb_handle_s *h, F &&f) {
         f();
         return NB_OK;
     } catch (const Error &e) {
-        if (h) h->last_error = e.what();
+        if (h) h->last_error = e.code == NB_ERR_CUDA ? e.what() + trace_report(h) : std::string(e.what());
         return e.code;
     } catch (const std::bad_alloc &) {
         if (h) h->last_error = "host allocation failed";
@@ -84,6 +85,21 @@ int nb_create(int device_id, nb_handle_t *handle) {
             h->get_address_range = (nb_get_address_range_fn)fn;     // optional: without it operand extents go unchecked
         // Shared-memory limits of the tensor-core kernels are a per-device setting; setting them here, with this
         // handle's device current, also loads every kernel's code before the first forward pass.
+        const char *tr = std::getenv("NEBULA_B200_TRACE");
+        if (tr && *tr && *tr != '0') {
+            fn = nullptr;
+            if (cudaGetDriverEntryPoint("cuStreamWriteValue32", &fn, cudaEnableDefault, &qres) == cudaSuccess &&
+                qres == cudaDriverEntryPointSuccess && fn) {
+                unsigned *hp = nullptr;
+                NB_CHECK_CUDA(cudaHostAlloc((void **)&hp, sizeof(unsigned), cudaHostAllocMapped));
+                *hp = 0;
+                void *dp = nullptr;
+                NB_CHECK_CUDA(cudaHostGetDevicePointer(&dp, hp, 0));
+                h->write_value = (nb_handle_s::write_value_fn)fn;
+                h->trace_host = hp;
+                h->trace_dev = (CUdeviceptr)dp;
+            }
+        }
         gemm_tc_prepare_device();
         conv_halo_prepare_device();
         elementwise_prepare_device();

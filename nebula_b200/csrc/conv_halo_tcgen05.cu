@@ -387,6 +387,7 @@ void conv_halo_tc(nb_handle_s *h, const GemmArgs &a) {
         throw Error(err.code, std::string(err.what()) + L.desc);
     }
     count_launch(h);
+    if (h->trace_host && !h->trace_names.empty()) h->trace_names.back() += L.desc;
     prof.finish();
 }
 

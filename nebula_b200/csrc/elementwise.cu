@@ -13,7 +13,25 @@ namespace nb {
 
 // NEBULA_B200_SYNC_LAUNCHES=1 in the environment waits for every kernel before returning, so that an asynchronous
 // device error is reported against the launch that caused it (debugging aid; off by default).
+namespace { thread_local const char *t_last_launch = ""; }
+
+void trace_launch(nb_handle_s *h) {
+    if (h->trace_names.size() > (1u << 20)) return;
+    h->trace_names.push_back(t_last_launch);
+    h->write_value((CUstream)h->stream, h->trace_dev, (cuuint32_t)h->trace_names.size(), 0);
+}
+std::string trace_report(nb_handle_s *h) {
+    if (!h->trace_host) return "";
+    const unsigned done = *h->trace_host;
+    std::string r = " [launch trace: " + std::to_string(done) + " of " + std::to_string(h->trace_names.size()) + " launches finished";
+    if (done > 0 && done <= h->trace_names.size()) r += "; last finished: #" + std::to_string(done) + " " + h->trace_names[done - 1];
+    for (unsigned i = done; i < h->trace_names.size() && i < done + 3; i++)
+        r += "; then #" + std::to_string(i + 1) + " " + h->trace_names[i];
+    return r + "]";
+}
+
 void check_launch(const char *what) {
+    t_last_launch = what;
     static const bool sync_launches = [] {
         const char *v = std::getenv("NEBULA_B200_SYNC_LAUNCHES");
         return v && *v && *v != '0';

@@ -788,6 +788,7 @@ void gemm_tc(nb_handle_s *h, const GemmArgs &a, bool three_pass) {
         throw Error(err.code, std::string(err.what()) + L.desc);    // an asynchronous fault is otherwise hard to place
     }
     count_launch(h);
+    if (h->trace_host && !h->trace_names.empty()) h->trace_names.back() += L.desc;
     prof.finish();
 }
 

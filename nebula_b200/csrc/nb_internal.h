@@ -72,6 +72,14 @@ struct nb_handle_s {
     std::vector<cudaEvent_t> event_pool;    // events are re-used across profiling windows
     std::unordered_map<std::string, std::unique_ptr<nb::LaunchRecord>> launch_cache;
     std::shared_ptr<nb::Arena> arena;
+    // Opt-in launch trace (NEBULA_B200_TRACE=1 when the handle is created): after every kernel the stream writes that
+    // launch's ordinal into page-locked host memory, so that after an asynchronous device error the message can
+    // name the last launch that finished and the one that did not.
+    typedef CUresult (*write_value_fn)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
+    write_value_fn write_value = nullptr;
+    volatile unsigned *trace_host = nullptr;
+    CUdeviceptr trace_dev = 0;
+    std::vector<std::string> trace_names;
     // device allocations seen by check_extent: [base, end) by base address
     std::map<uintptr_t, uintptr_t> known_ranges;
 };
@@ -291,8 +299,14 @@ struct ProfileScope {
 void encode_tensor_map(nb_handle_s *h, CUtensorMap *tm, const void *base, int rank, const cuuint64_t *dims,
                        const cuuint64_t *strides_bytes, const cuuint32_t *box, const cuuint32_t *elem_strides);
 
-inline void count_launch(nb_handle_s *h, int n = 1) { h->launches += (unsigned long long)n; }
+void trace_launch(nb_handle_s *h);
+inline void count_launch(nb_handle_s *h, int n = 1) {
+    h->launches += (unsigned long long)n;
+    if (h->trace_host) trace_launch(h);
+}
 void check_launch(const char *what);
+// what the launch trace knows about where the stream got to (empty when tracing is off)
+std::string trace_report(nb_handle_s *h);
 
 // Fails with NB_ERR_INVALID_ARG when [p + lo_bytes, p + hi_bytes) is not inside ONE device allocation (as the driver
 // reports it for p).  Pointers the driver does not know as an allocation (module globals, host memory) pass.

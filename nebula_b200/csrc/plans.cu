@@ -283,7 +283,11 @@ void ConvPlan::forward(const float *x, float *y, const ForwardOpts &o) {
         a.b = w.hi.p;
         a.b_lo = w.lo.p;
         // few input channels: the generic kernel would re-load the activations once per tap from L2
-        bool halo = pth == PATH_TC && (d.channels <= 64 || (d.channels <= 128 && d.filters <= 128)) &&
+        static const bool halo_on = [] {        // NEBULA_B200_HALO=0 routes these layers through the generic kernel
+            const char *v = std::getenv("NEBULA_B200_HALO");
+            return !(v && *v == '0');
+        }();
+        bool halo = halo_on && pth == PATH_TC && (d.channels <= 64 || (d.channels <= 128 && d.filters <= 128)) &&
                     conv_halo_supported(h, a);
         if (halo) {
             const int bh = OH >= 16 ? 16 : 8;

@@ -38,13 +38,38 @@ def lstm_bn_net():
     return b.build("normal")
 
 
+def rnn_net():
+    """Two vanilla RNN layers (the second batch-normalised) and a projection: rnn_layer.cc:91-141."""
+    b = NetBuilder("rnn", 3, input_size=12, time_steps=5, bias_init="bias_n01")
+    b.rnn(8, "tanh", bound=0.4).rnn(6, "leaky", bn=True, bound=0.4).connected(7, "linear", init="uniform", bound=0.4).softmax()
+    return b.build("normal")
+
+
+def lstm_act_net():
+    """LSTM whose eight gate layers carry a non-linear section activation (lstm_layer.cc:252-282)."""
+    b = NetBuilder("lstm_act", 3, input_size=10, time_steps=4, bias_init="bias_n01")
+    b.lstm(6, act="tanh", bound=0.4).lstm(5, act="leaky", bn=True, bound=0.4)
+    b.connected(7, "linear", init="uniform", bound=0.4).softmax()
+    return b.build("normal")
+
+
+def dbn_net():
+    """[rbm] layers at inference (rbm_layer.cc:345-374) and a linear classifier, as in benchmarks/dbn_*/network.cfg."""
+    b = NetBuilder("dbn", 4, 3, 6, 5, bias_init="bias_n01")
+    b.rbm(20, "logistic").rbm(12, "logistic").rbm(8, "tanh").connected(5, "linear").softmax()
+    return b.build()
+
+
 CASES = {"toy_convnet": (toy_convnet, 101), "shortcuts": (shortcut_net, 102), "tiny_lstm": (tiny_lstm, 103),
-         "lstm_bn": (lstm_bn_net, 104)}
+         "lstm_bn": (lstm_bn_net, 104), "rnn": (rnn_net, 105), "lstm_act": (lstm_act_net, 106), "dbn": (dbn_net, 107)}
 
 
 def main():
     out_dir = Path(__file__).resolve().parent
+    only = set(sys.argv[1:])
     for name, (make, seed) in CASES.items():
+        if only and name not in only:
+            continue
         wl = make()
         w = wl.make_weights(seed)
         x = wl.make_input(seed + 1000)

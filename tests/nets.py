@@ -1,6 +1,6 @@
 """Small networks shared by the CPU and GPU tests (built with the same builders
 as the benchmark configurations)."""
-from nebula_b200.workloads import NetBuilder, alexnet, lstm2, resnet50, vgg16
+from nebula_b200.workloads import NetBuilder, alexnet, dbn, lstm2, resnet50, rnn2, vgg16
 
 
 def toy_convnet(batch=3):
@@ -30,8 +30,28 @@ def tiny_lstm(batch=4, time_steps=6):
     return lstm2(batch=batch, time_steps=time_steps, input_size=64, hidden=32, classes=50)
 
 
+def tiny_rnn(batch=4, time_steps=5):
+    """Two [rnn] layers (tanh, then batch-normalised leaky) and a projection, wide enough for the tensor-core path."""
+    b = NetBuilder("tiny_rnn", batch, input_size=64, time_steps=time_steps, bias_init="bias_n01")
+    b.rnn(64, "tanh", bound=0.2).rnn(32, "leaky", bn=True, bound=0.2).connected(50, "linear", init="uniform", bound=0.2)
+    return b.build("normal")
+
+
+def tiny_lstm_act(batch=4, time_steps=5):
+    """LSTM layers whose gate layers carry a non-linear section activation."""
+    b = NetBuilder("tiny_lstm_act", batch, input_size=64, time_steps=time_steps, bias_init="bias_n01")
+    b.lstm(32, act="tanh", bound=0.2).lstm(32, act="leaky", bn=True, bound=0.2)
+    b.connected(50, "linear", init="uniform", bound=0.2)
+    return b.build("normal")
+
+
+def tiny_dbn(batch=6):
+    return dbn(batch=batch, height=8, width=8, channels=3, hidden=(96, 64, 32), classes=10)
+
+
 def small_alexnet(batch=2):
     return alexnet(batch=batch)
 
 
-NETS = {"toy": toy_convnet, "tiny_vgg": tiny_vgg, "mid_vgg": mid_vgg, "tiny_resnet": tiny_resnet, "tiny_lstm": tiny_lstm}
+NETS = {"toy": toy_convnet, "tiny_vgg": tiny_vgg, "mid_vgg": mid_vgg, "tiny_resnet": tiny_resnet, "tiny_lstm": tiny_lstm,
+        "tiny_rnn": tiny_rnn, "tiny_lstm_act": tiny_lstm_act, "tiny_dbn": tiny_dbn}
