@@ -8,10 +8,13 @@ with TF32 tensor-core contractions, on N B200 GPUs of one node.
 A step is one forward pass of the whole network over the batch (each rank runs
 its contiguous slice with replicated weights; for N>1 the step ends with the one
 collective of the path, an NCCL all-gather of the logits).  `value` is images/s
-with the batch resident in HBM; `e2e` is the same metric through the C-ABI host
-call (pinned host batch copied in, probabilities copied out, every step).
+with the batch resident in HBM; `e2e` is the same metric through the C-ABI
+hand-off calls (nb_network_submit_u8 / nb_network_submit_host + nb_network_wait):
+every step copies that step's pinned host batch in -- decoded 8-bit images for
+the image networks, as the reference holds them before its float conversion --
+and the probabilities out, the copy of step i+1 overlapping the pass of step i.
 Inputs and weights are seeded synthetic tensors with ImageNet shapes and value
-range (uniform [0,1) images, He-normal weights).
+range (uniform 8-bit images / 255, He-normal weights).
 
 `--impl reference` times the reference's own CPU implementation (the binary
 under oracle/_ref, compiled from the reference sources) on a bounded sample of
@@ -89,6 +92,17 @@ class ClockSampler:
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
                 "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def ncu_traffic(workload: str, math: str, world: int, kernel: str):
+    """DRAM bytes per launch of `kernel` from the table of ncu captures (nebula_b200/ncu_traffic.json), or (None, why)."""
+    p = ROOT / "nebula_b200" / "ncu_traffic.json"
+    if world != 1 or not p.exists():
+        return None, "no capture for this configuration"
+    for row in json.loads(p.read_text()).get("captures", []):
+        if row["workload"] == workload and row["math"] == math and row["kernel"] == kernel:
+            return row["dram_bytes_per_launch"], row["source"]
+    return None, "no capture for this configuration"
 
 
 def make_workload(name: str, batch: int):
@@ -187,26 +201,57 @@ def gpu_arm(args):
     weights = full.make_weights(WEIGHT_SEED)
     net.load_weights(weights)
     del weights
-    x_host_full = full.make_input(INPUT_SEED)
-    x_host = sharding.shard_input(x_host_full, world, rank, full.recurrent)
-    del x_host_full
+    images = not full.recurrent
+    if images:
+        # decoded 8-bit images [B,H,W,C] (BGR), and the reference's float conversion of the same images
+        # (models/networks/convolutional.cc:386-398) for the device-resident leg: both legs compute the same thing
+        Bf, Cf, Hf, Wf = full.input_shape
+        u8_full = np.random.default_rng(INPUT_SEED).integers(0, 256, size=(Bf, Hf, Wf, Cf), dtype=np.uint8)
+        u8 = np.ascontiguousarray(u8_full[lo:hi])
+        del u8_full
+        x_host = (u8.astype(np.float64) / 255.0).astype(np.float32).transpose(0, 3, 1, 2)
+        x_host = np.ascontiguousarray(x_host[:, ::-1] if Cf == 3 else x_host)
+        x_pin = torch.from_numpy(u8).pin_memory()
+    else:
+        x_host_full = full.make_input(INPUT_SEED)
+        x_host = sharding.shard_input(x_host_full, world, rank, full.recurrent)
+        del x_host_full
+        x_pin = torch.from_numpy(x_host).pin_memory()
     x_dev = torch.from_numpy(x_host).to(dev)
-    x_pin = torch.from_numpy(x_host).pin_memory()
-    out_pin = torch.empty(net.output_size, dtype=torch.float32).pin_memory()
+    out_pins = [torch.empty(net.output_size, dtype=torch.float32).pin_memory() for _ in range(2)]
     classes = full.classes
     rows = net.logits_size // classes
+    pending = []        # logits all-gathers in flight (they overlap the next step's pass)
+
+    def gather_logits():
+        """The one collective of the path, started behind the pass and not waited for until two steps later."""
+        lg = net.logits(device=dev).view(rows, classes)
+        if full.recurrent:
+            lg = lg.view(-1, my, classes).permute(1, 0, 2).reshape(my, -1).contiguous()
+        pending.append(sharding.gather_rows(lg, batch, world, rank, async_op=True))
+        while len(pending) > 2:
+            pending.pop(0).wait()
+
+    def drain():
+        while pending:
+            pending.pop(0).wait()
 
     def step_device():
         net.forward(x_dev)
         if world > 1:
-            lg = net.logits(device=dev).view(rows, classes)
-            if full.recurrent:
-                sharding.gather_time_major(lg.view(-1, my, classes), batch, world, rank)
-            else:
-                sharding.gather_rows(lg, batch, world, rank)
+            gather_logits()
+
+    step_no = [0]
 
     def step_host():
-        net.forward_host(x_pin, out_pin)
+        out = out_pins[step_no[0] & 1]
+        step_no[0] += 1
+        if images:
+            net.submit_u8(x_pin, out)
+        else:
+            net.submit_host(x_pin, out)
+        if world > 1:
+            gather_logits()
 
     def barrier():
         torch.cuda.synchronize()
@@ -220,6 +265,8 @@ def gpu_arm(args):
         e0.record()
         for _ in range(steps):
             fn()
+        net.wait()          # pipelined submissions: every output is in host memory
+        drain()             # ... and every gather has finished (the waits are stream-side)
         e1.record()
         barrier()
         ms = e0.elapsed_time(e1)
@@ -230,23 +277,35 @@ def gpu_arm(args):
         return ms
 
     W, K = max(3, args.warmup), max(1, args.steps)
+    # N > 1: a pass is a few dozen launches of a millisecond or two in total, so it is replayed as one CUDA graph and
+    # the per-kernel event timing (which needs the kernels launched one by one) runs as a second region of K steps.
+    # N = 1: one region, kernels launched one by one with their event pairs, value and roofline from the same steps.
+    separate_profile = world > 1
+    net.set_graph(separate_profile)
     for _ in range(W):
         step_device()
+    drain()
     handle.synchronize()
 
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
     launches0 = handle.launch_count()
-    handle.profile_begin()
+    if not separate_profile:
+        handle.profile_begin()
     total_ms = timed(step_device, K)
-    prof = handle.profile_end()
     launches = handle.launch_count() - launches0
+    if separate_profile:
+        handle.profile_begin()
+        timed(step_device, K)
+    prof = handle.profile_end()
     clocks = sampler.stop() if rank == 0 else None
     handle.synchronize()
 
-    for _ in range(2):
+    for _ in range(3):
         step_host()
+    net.wait()
+    drain()
     e2e_ms = timed(step_host, K)
     handle.synchronize()
 
@@ -272,10 +331,9 @@ def gpu_arm(args):
         d_ms, d_fl, d_n = (prof[f] for f in kernels[dom])
         o_ms, o_fl, o_n = (prof[f] for f in kernels[other])
         achieved = d_fl / (d_ms / 1e3) / 1e12 if d_ms > 0 else 0.0
-        # dram__bytes_read + dram__bytes_write per launch of the generic kernel, from one ncu pass over a
-        # forward pass of this exact workload (profiles/vgg16_b256_launch_list.md); other workloads: not captured
-        traffic = 815.2e6 if (wl_name == "vgg16" and batch == 256 and world == 1 and args.math == "tf32"
-                              and dom == "gemm_tf32_tcgen05_kernel") else None
+        # dram__bytes_read + dram__bytes_write per launch of the dominant kernel: not something a run can measure on
+        # itself; taken from the table of ncu captures kept with the package (null when this workload has none)
+        traffic, traffic_source = ncu_traffic(f"{wl_name}_b{batch}", args.math, world, dom)
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
             try:
@@ -294,13 +352,19 @@ def gpu_arm(args):
                        "parallelism": f"batch-sharded replicas x{world}, logits all-gather" if world > 1 else "single GPU",
                        "l2": "inputs and activations larger than L2 (no flush needed)",
                        "storage": "fp32, NHWC internal"},
-            "e2e": {"value": round(e2e, 2), "unit": UNIT[wl_name], "h2d_bytes_per_step": int(x_pin.numel() * 4 * world),
-                    "d2h_bytes_per_step": int(out_pin.numel() * 4 * world)},
+            "e2e": {"value": round(e2e, 2), "unit": UNIT[wl_name],
+                    "h2d_bytes_per_step": int(x_pin.numel() * x_pin.element_size() * world),
+                    "d2h_bytes_per_step": int(out_pins[0].numel() * 4 * world),
+                    "input": "decoded 8-bit images, pinned" if images else "fp32 sequences, pinned",
+                    "api": "nb_network_submit_u8 + nb_network_wait" if images else "nb_network_submit_host + nb_network_wait",
+                    "pipelined": "copy of step i+1 overlaps the pass of step i (two device input slots)"},
             "gpu_launches": launches,
             "clocks": clocks,
             "roofline": {"bound": "tensor", "achieved": round(achieved, 2), "peak": round(tf32_peak, 1), "unit": "TFLOP/s",
                          "frac": round(achieved / tf32_peak, 4) if tf32_peak else None, "traffic": traffic,
-                         "traffic_unit": "bytes per launch (ncu dram read+write)",
+                         "traffic_unit": "bytes per launch (ncu dram read+write)", "traffic_source": traffic_source,
+                         "timed_in": "a second region of the same K steps, kernels launched one by one" if separate_profile
+                                     else "the region `value` comes from",
                          "kernel": dom,
                          "launches_per_step": d_n / K, "kernel_ms_per_step": round(d_ms / K, 4),
                          "other_tensor_kernel": {"kernel": other, "launches_per_step": o_n / K,

@@ -16,7 +16,7 @@
 // Replaces the same reference code as the generic kernel
 // (models/layers/convolutional_layer.cu:47-70, common/utils.cu:34-74) for these
 // layers; same fused epilogue (batch-norm/bias/activation/TF32 rounding, optional
-// 2x2/2 max-pool).  Warp roles: 0 TMA producer, 1 and 10 MMA issuers (one per half), 2-9 epilogue.
+// 2x2/2 max-pool).  Warp roles: 0 TMA producer, 1 MMA issuer, 2-9 epilogue.
 // Every wait is bounded, as in the generic kernel.
 #include <algorithm>
 #include <cstring>
@@ -55,7 +55,7 @@ struct HCfg {
 };
 
 template <int BLOCK_N>
-__global__ void __launch_bounds__(352, 1) conv3x3_halo_tcgen05_kernel(const __grid_constant__ HaloParams p) {
+__global__ void __launch_bounds__(320, 1) conv3x3_halo_tcgen05_kernel(const __grid_constant__ HaloParams p) {
     using C = HCfg<BLOCK_N>;
     constexpr int B_RING = C::B_RING;
     extern __shared__ uint8_t smem_raw[];
@@ -77,10 +77,9 @@ __global__ void __launch_bounds__(352, 1) conv3x3_halo_tcgen05_kernel(const __gr
     const uint32_t tmem_cols = (2 * acc_cols <= 128) ? 128 : (2 * acc_cols <= 256 ? 256 : 512);
 
     if (threadIdx.x == 0) {
-        // one MMA-issuing warp per accumulator half: each commits once per ring slot / accumulator set
-        for (int s = 0; s < A_RING; s++) { mbar_init(&a_full[s], 1); mbar_init(&a_empty[s], p.halves); }
-        for (int s = 0; s < B_RING; s++) { mbar_init(&b_full[s], 1); mbar_init(&b_empty[s], p.halves); }
-        for (int a = 0; a < 2; a++) { mbar_init(&acc_full[a], p.halves); mbar_init(&acc_empty[a], 256); }
+        for (int s = 0; s < A_RING; s++) { mbar_init(&a_full[s], 1); mbar_init(&a_empty[s], 1); }
+        for (int s = 0; s < B_RING; s++) { mbar_init(&b_full[s], 1); mbar_init(&b_empty[s], 1); }
+        for (int a = 0; a < 2; a++) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 256); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -143,12 +142,10 @@ __global__ void __launch_bounds__(352, 1) conv3x3_halo_tcgen05_kernel(const __gr
             }
         }
         __syncwarp();
-    } else if (warp == 1 || warp == 10) {
-        // ------------------------------------------------------- MMA issuers
-        // Short N=64/128 MMAs are bound by the issue rate of one thread, so each 128-row half has its own
-        // issuing warp (warp 1: half 0, warp 10: half 1); both read the same operand rings.
-        const int hf = warp == 1 ? 0 : 1;
-        if (hf < p.halves && elect_one()) {
+    } else if (warp == 1) {
+        // -------------------------------------------------------- MMA issuer
+        // One thread issues the MMAs of both 128-row halves: per tap, the two halves share the weight tile.
+        if (elect_one()) {
             constexpr uint32_t idesc = make_idesc(BLOCK_M, BLOCK_N);
             int sa = 0, sb = 0, acc = 0;
             uint32_t pa = 0, pb = 0, acc_phase = 0;
@@ -167,11 +164,13 @@ __global__ void __launch_bounds__(352, 1) conv3x3_halo_tcgen05_kernel(const __gr
                         const uint32_t b_lo = smem_desc_lo(smem_u32(b_ring + sb * C::B_BYTES));
                         const int kh = tap / 3, kw = tap - kh * 3;
                         const uint32_t a_lo = smem_desc_lo(a_base + (uint32_t)((kh * p.wt + kw) * 128));
+                        for (int hf = 0; hf < p.halves; hf++) {
 #pragma unroll
-                        for (int k = 0; k < BLOCK_K / UMMA_K; k++)      // +32 bytes per K step = +2 in the descriptor;
-                            umma_tf32(d_tmem + (uint32_t)(hf * BLOCK_N),    // the second half starts 128 rows = 16 KiB further on
-                                      smem_desc(a_lo + hf * (BLOCK_M * 128 >> 4) + 2 * k), smem_desc(b_lo + 2 * k), idesc,
-                                      (cb | tap | k) != 0);
+                            for (int k = 0; k < BLOCK_K / UMMA_K; k++)      // +32 bytes per K step = +2 in the descriptor;
+                                umma_tf32(d_tmem + (uint32_t)(hf * BLOCK_N),    // the second half starts 128 rows = 16 KiB further on
+                                          smem_desc(a_lo + hf * (BLOCK_M * 128 >> 4) + 2 * k), smem_desc(b_lo + 2 * k), idesc,
+                                          (cb | tap | k) != 0);
+                        }
                         umma_commit(&b_empty[sb]);
                         if (++sb == B_RING) { sb = 0; pb ^= 1; }
                     }
@@ -380,7 +379,7 @@ void conv_halo_tc(nb_handle_s *h, const GemmArgs &a) {
     }
     const HaloLaunch &L = static_cast<const HaloLaunch &>(*it->second);
     ProfileScope prof(h, 2, L.flops);
-    L.kernel<<<L.grid, 352, L.smem, h->stream>>>(L.p);
+    L.kernel<<<L.grid, 320, L.smem, h->stream>>>(L.p);
     try {
         check_launch("conv3x3_halo_tcgen05_kernel");
     } catch (const Error &err) {

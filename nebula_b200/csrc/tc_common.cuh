@@ -192,6 +192,9 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
 constexpr uint32_t SMEM_DESC_HI = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);
 __device__ __forceinline__ uint32_t smem_desc_lo(uint32_t smem_addr) { return ((smem_addr >> 4) & 0x3FFF) | (1u << 16); }
 __device__ __forceinline__ uint64_t smem_desc(uint32_t lo) { return ((uint64_t)SMEM_DESC_HI << 32) | lo; }
+// (An operand read at a row offset -- a start address off the pattern's 1024-byte repeat -- keeps base offset 0 as
+// long as the data was laid down by TMA: both sides derive the swizzle phase from the absolute shared-memory address.
+// Measured: a non-zero base offset on such a descriptor garbles the product.)
 
 // Instruction descriptor for kind::tf32: D=f32 (bits 4-5 = 1), A=B=tf32 (bits
 // 7-9, 10-12 = 2), both K-major (bits 15,16 = 0), N>>3 at bit 17, M>>4 at bit 24.

@@ -38,26 +38,42 @@ def shard_input(x, world: int, rank: int, recurrent: bool):
     return np.ascontiguousarray(out) if isinstance(out, np.ndarray) else out.contiguous()
 
 
-def gather_rows(local, total_rows: int, world: int, rank: int, group=None):
+class _Gather:
+    """An all-gather in flight: wait() returns the [total_rows, classes] tensor."""
+
+    def __init__(self, work, out, sizes, mx):
+        self.work, self.out, self.sizes, self.mx = work, out, sizes, mx
+
+    def wait(self):
+        import torch
+        if self.work is not None:
+            self.work.wait()        # orders the caller's current stream behind the collective; no host block
+        if all(s == self.mx for s in self.sizes):
+            return self.out
+        return torch.cat([self.out[r * self.mx:r * self.mx + s] for r, s in enumerate(self.sizes)], 0)
+
+
+def gather_rows(local, total_rows: int, world: int, rank: int, group=None, async_op: bool = False):
     """All-gathers per-rank [rows_r, classes] tensors into [total_rows, classes]
     on every rank (rows in global batch order).  Uneven shards are padded to the
-    largest shard for the collective and trimmed afterwards."""
+    largest shard for the collective and trimmed afterwards.  With async_op the
+    collective is only started (it overlaps whatever the caller queues next) and
+    an object whose wait() gives the result is returned."""
     import torch
     import torch.distributed as dist
     sizes = shard_sizes(total_rows, world)
     assert local.shape[0] == sizes[rank], (local.shape, sizes, rank)
     if world == 1:
-        return local
+        return _Gather(None, local, sizes, sizes[0]) if async_op else local
     classes = local.shape[1]
     mx = max(sizes)
     if local.shape[0] != mx:
         pad = torch.zeros((mx - local.shape[0], classes), dtype=local.dtype, device=local.device)
         local = torch.cat([local, pad], 0)
     out = torch.empty((world * mx, classes), dtype=local.dtype, device=local.device)
-    dist.all_gather_into_tensor(out, local.contiguous(), group=group)
-    if all(s == mx for s in sizes):
-        return out
-    return torch.cat([out[r * mx:r * mx + sizes[r]] for r in range(world)], 0)
+    work = dist.all_gather_into_tensor(out, local.contiguous(), group=group, async_op=async_op)
+    g = _Gather(work if async_op else None, out, sizes, mx)
+    return g if async_op else g.wait()
 
 
 def gather_time_major(local, total_batch: int, world: int, rank: int, group=None):
