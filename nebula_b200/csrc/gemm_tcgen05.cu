@@ -654,8 +654,10 @@ std::unique_ptr<TcLaunch> build_launch(nb_handle_s *h, const GemmArgs &a, bool t
     }
     p.n_tiles = (a.N + block_n - 1) / block_n;
     p.m_fastest = (!a.a_is_conv && !gather && (size_t)a.N * a.Kc * 4 > ((size_t)48 << 20)) ? 1 : 0;
-    // accumulation chains of at most 512 (TF32) / 128 (3xTF32) K elements in the tensor core
-    p.kb_per_part = !promote ? p.kb_per_split : (three_pass ? 4 : 16);
+    // accumulation chains of at most 512 (TF32) / 32 (3xTF32) K elements in the tensor core: every accumulating MMA
+    // truncates the running sum (a shrink of about 6e-8 per step that adds up layer after layer); a 3xTF32 K block
+    // is 12 MMAs, 11 of them accumulating
+    p.kb_per_part = !promote ? p.kb_per_split : (three_pass ? 1 : 16);
     p.parts = (p.kb_per_split + p.kb_per_part - 1) / p.kb_per_part;
 
     p.gather = gather ? 1 : 0;

@@ -347,3 +347,30 @@ void nbo_rnn_forward(const float *x, int T, int B, int in, int H, const nbo_fc_b
     }
     free(a); free(hd); free(state);
 }
+
+/* ------------------------------------------------------------------ GEMM
+ * gemm<T> of the operator library (common/gemm.h:51-147), row-major with leading
+ * dimensions: C *= beta, then one of four loop nests by transpose flags -- nn and
+ * tn accumulate a_p * B[k][j] into C directly (a_p = alpha * A), nt and tt form
+ * sum += alpha * A * B in a float and add it to C once.  The reference splits the
+ * rows of C over threads; rows are independent, so one thread gives the same bits. */
+void nbo_gemm(int TA, int TB, int M, int N, int K, float alpha, const float *A, int lda, const float *B, int ldb,
+              float beta, float *C, int ldc) {
+    for (int i = 0; i < M; i++)
+        for (int j = 0; j < N; j++) C[(long)i * ldc + j] *= beta;
+    for (int i = 0; i < M; i++) {
+        if (!TB) {
+            for (int k = 0; k < K; k++) {
+                float a_p = alpha * (TA ? A[(long)k * lda + i] : A[(long)i * lda + k]);
+                for (int j = 0; j < N; j++) C[(long)i * ldc + j] += a_p * B[(long)k * ldb + j];
+            }
+        } else {
+            for (int j = 0; j < N; j++) {
+                float sum = 0;
+                for (int k = 0; k < K; k++)
+                    sum += alpha * (TA ? A[(long)k * lda + i] : A[(long)i * lda + k]) * B[(long)j * ldb + k];
+                C[(long)i * ldc + j] += sum;
+            }
+        }
+    }
+}

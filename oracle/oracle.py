@@ -136,6 +136,13 @@ def lstm_forward(x, blobs, H, act="linear", has_bn=False):
     return out, cell
 
 
+def gemm(ta, tb, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc):
+    """gemm<T> (common/gemm.h:111-147) on flat row-major buffers; returns the updated copy of C."""
+    A, B, C = _f32(A).ravel(), _f32(B).ravel(), _f32(C).ravel().copy()
+    lib().nbo_gemm(int(ta), int(tb), M, N, K, ctypes.c_float(alpha), _fp(A), lda, _fp(B), ldb, ctypes.c_float(beta), _fp(C), ldc)
+    return C
+
+
 def rnn_forward(x, blobs, H, act, has_bn=False):
     """x [T,B,in] time-major; blobs = 3 dicts in file order input, hidden, output gate.  Returns out [T,B,H]."""
     x = _f32(x)

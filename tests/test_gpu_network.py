@@ -4,7 +4,7 @@ import numpy as np
 import pytest
 
 from tests.nets import NETS, small_alexnet
-from tests.util import NET_TOL, assert_close, rel_err
+from tests.util import NET_TOL, NET_TOL_EXCEPTIONS, assert_close, net_tol, rel_err
 
 pytestmark = pytest.mark.gpu
 
@@ -51,7 +51,8 @@ def test_network_tensor_core_modes(handle, name, mode):
     errs = [rel_err(net.layer_output(i, rows), r) for i, r in enumerate(refs)]
     logits = net.logits()
     li = max(i for i in range(net.num_layers) if net.layer_info(i)["type"] == "connected")
-    e = assert_close(logits, refs[li], mode, f"{name} logits (per-layer errs {['%.1e' % v for v in errs]})", rows=rows, tol=NET_TOL)
+    e = assert_close(logits, refs[li], mode, f"{name} logits (per-layer errs {['%.1e' % v for v in errs]})", rows=rows,
+                     tol={mode: net_tol(name, mode)})
     print(f"{name} {mode}: logits err {e:.2e}; per-layer {['%.1e' % v for v in errs]}")
     ref_l = refs[li].reshape(rows, -1)
     assert (logits.reshape(rows, -1).argmax(1) == ref_l.argmax(1)).all(), "argmax differs"

@@ -215,10 +215,19 @@ def test_gemm_operator(handle, ta, tb):
     A = rng.standard_normal((K, M) if ta else (M, K)).astype(np.float32)
     Bm = rng.standard_normal((N, K) if tb else (K, N)).astype(np.float32)
     Cm = rng.standard_normal((M, N)).astype(np.float32)
-    ref = 0.5 * ((A.T if ta else A).astype(np.float64) @ (Bm.T if tb else Bm).astype(np.float64)) + 1.0 * Cm
-    out = handle.gemm(ta, tb, M, N, K, 0.5, _t(A), A.shape[1], _t(Bm), Bm.shape[1], 1.0, _t(Cm), N).cpu().numpy()
+    from oracle import oracle as O
+    # padded leading dimensions, as the operator's callers may pass them
+    lda, ldb, ldc = A.shape[1] + 3, Bm.shape[1] + 5, N + 2
+    Ap = np.zeros((A.shape[0], lda), np.float32); Ap[:, :A.shape[1]] = A
+    Bp = np.zeros((Bm.shape[0], ldb), np.float32); Bp[:, :Bm.shape[1]] = Bm
+    Cp = np.full((M, ldc), 7.0, np.float32); Cp[:, :N] = Cm
+    ref = O.gemm(ta, tb, M, N, K, 0.5, Ap, lda, Bp, ldb, 1.0, Cp, ldc).reshape(M, ldc)       # the reference's gemm<T>
+    out = handle.gemm(ta, tb, M, N, K, 0.5, _t(Ap), lda, _t(Bp), ldb, 1.0, _t(Cp), ldc).cpu().numpy()
     handle.synchronize()
-    assert rel_err(out, ref) < 1e-5
+    assert np.array_equal(out[:, N:], Cp[:, N:]), "columns beyond N must not be touched"
+    assert rel_err(out[:, :N], ref[:, :N]) < 1e-5
+    f64 = 0.5 * ((A.T if ta else A).astype(np.float64) @ (Bm.T if tb else Bm).astype(np.float64)) + 1.0 * Cm
+    assert rel_err(out[:, :N], f64) < 1e-5
 
 
 def test_layout_roundtrip(handle):
