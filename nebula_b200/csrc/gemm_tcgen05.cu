@@ -71,6 +71,11 @@ struct TcParams {
     // After every kb_per_part K blocks the partial sums are promoted to registers (round-to-nearest adds)
     // and the TMEM accumulator restarts; parts = number of such partial sums per tile (1: no promotion).
     int kb_per_part, parts;
+    // Ring stages of `cbs` K blocks (1 or 2).  One TMA request costs its issuing thread a few hundred cycles whatever
+    // its size, and a narrow tile's K block is only 180-350 cycles of MMAs, so convolutions with 64-128 input
+    // channels fetch two 32-channel slices of a tap per request: the A map then has the slice index as a fifth
+    // dimension (tm_a is 5-D, tm_b 4-D), a stage is [A0 | A1 | B0 | B1], `stages` of them fit the ring.
+    int cbs, stages;
     EpiParams e;                // fused epilogue
     // gather mode: warps 6-9 build the A tile in shared memory from a strided activation tensor
     // (channel counts TMA cannot address, e.g. the 3-channel input layer); rows are output pixels
@@ -100,10 +105,13 @@ template <int BLOCK_N, bool THREE, bool PROMOTE>
 __global__ void __launch_bounds__(Cfg<BLOCK_N, THREE>::MAX_THREADS, 1)
 gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
     using C = Cfg<BLOCK_N, THREE>;
-    constexpr int STAGES = C::STAGES;
+    constexpr int STAGES = C::STAGES;                   // barrier slots; the ring uses the first p.stages of them
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    // per stage: [A | B | (A_lo | B_lo)]
+    // per stage: [A | B | (A_lo | B_lo)], or [A0 | A1 | B0 | B1] with two K blocks per stage
+    const int cbs = THREE ? 1 : p.cbs;
+    const int stages = p.stages;
+    const int stage_bytes = C::STAGE_BYTES * cbs;
     uint8_t *out_stage = smem + STAGES * C::STAGE_BYTES;      // 2 x [128 rows][32 floats], 128B-swizzled
     uint64_t *bars = (uint64_t *)(out_stage + 2 * C::OUT_STAGE_BYTES);
     uint64_t *full = bars;                    // TMA -> (splitter or MMA)
@@ -144,9 +152,9 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
         const int box_rows = p.gather ? BLOCK_M : p.bw * p.bh * p.bn;
         if (box_rows < BLOCK_M) {
             const int tail16 = (BLOCK_M - box_rows) * 8;          // 16-byte chunks per stage tail
-            for (int i = threadIdx.x; i < STAGES * tail16; i += blockDim.x) {
+            for (int i = threadIdx.x; i < stages * tail16; i += blockDim.x) {      // (two-block stages only take full boxes)
                 const int s = i / tail16, c = i - s * tail16;
-                reinterpret_cast<float4 *>(smem + s * C::STAGE_BYTES + box_rows * 128)[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+                reinterpret_cast<float4 *>(smem + s * stage_bytes + box_rows * 128)[c] = make_float4(0.f, 0.f, 0.f, 0.f);
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         }
@@ -178,29 +186,34 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
                 const int kb_end = min(kb0 + p.kb_per_split, p.num_k_blocks);      // the last split may be shorter
                 int tap = kb0 / p.c_blocks, cb = kb0 - tap * p.c_blocks;
                 int kh = tap / p.ksize_w, kw = tap - kh * p.ksize_w;
-                const uint32_t tx_bytes = (uint32_t)((p.gather ? 0 : p.tx_bytes_a) + C::B_STAGE_BYTES * (THREE ? 2 : 1));
-                for (int kb = kb0; kb < kb_end; kb++) {
+                const uint32_t tx_bytes = (uint32_t)(((p.gather ? 0 : p.tx_bytes_a) + C::B_STAGE_BYTES * (THREE ? 2 : 1)) * cbs);
+                for (int kb = kb0; kb < kb_end; kb += cbs) {
                     if (!(ok = mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status))) break;
-                    uint8_t *sa = smem + stage * C::STAGE_BYTES;
-                    uint8_t *sb = sa + A_STAGE_BYTES;
+                    uint8_t *sa = smem + stage * stage_bytes;
+                    uint8_t *sb = sa + A_STAGE_BYTES * cbs;
                     mbar_expect_tx(&full[stage], tx_bytes);
-                    if (!p.gather) tma_load_4d(sa, &p.tm_a, &full[stage], cb * BLOCK_K, w0 + kw, h0 + kh, n0);
-                    tma_load_3d(sb, &p.tm_b, &full[stage], cb * BLOCK_K, n_tile * BLOCK_N, tap);
-                    if (THREE)
-                        tma_load_3d(sb + C::B_STAGE_BYTES + A_STAGE_BYTES, &p.tm_b_lo, &full[stage], cb * BLOCK_K,
-                                    n_tile * BLOCK_N, tap);
-                    if (++cb == p.c_blocks) {
+                    if (cbs == 2) {
+                        tma_load_5d(sa, &p.tm_a, &full[stage], 0, w0 + kw, h0 + kh, n0, cb);
+                        tma_load_4d(sb, &p.tm_b, &full[stage], 0, n_tile * BLOCK_N, cb, tap);
+                    } else {
+                        if (!p.gather) tma_load_4d(sa, &p.tm_a, &full[stage], cb * BLOCK_K, w0 + kw, h0 + kh, n0);
+                        tma_load_3d(sb, &p.tm_b, &full[stage], cb * BLOCK_K, n_tile * BLOCK_N, tap);
+                        if (THREE)
+                            tma_load_3d(sb + C::B_STAGE_BYTES + A_STAGE_BYTES, &p.tm_b_lo, &full[stage], cb * BLOCK_K,
+                                        n_tile * BLOCK_N, tap);
+                    }
+                    if ((cb += cbs) == p.c_blocks) {
                         cb = 0; tap++;
                         if (++kw == p.ksize_w) { kw = 0; kh++; }
                     }
-                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                    if (++stage == stages) { stage = 0; phase ^= 1; }
                 }
             }
             // Tail: the MMA warp's last release of every stage (an mbarrier arrive that the tensor core performs
             // when those MMAs retire) must have landed in this CTA's shared memory before the CTA may exit.
-            for (int i = 0; i < STAGES && ok; i++) {
+            for (int i = 0; i < stages && ok; i++) {
                 ok = mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status);
-                if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                if (++stage == stages) { stage = 0; phase ^= 1; }
             }
         }
         __syncwarp();
@@ -219,7 +232,7 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
                 uint32_t d_tmem = tmem_base + (uint32_t)(acc * BLOCK_N);
                 int kb_in_part = 0;
                 const int tile_kb = min(p.kb_per_split, p.num_k_blocks - (tile % p.k_splits) * p.kb_per_split);
-                for (int kb = 0; kb < tile_kb; kb++, kb_in_part++) {
+                for (int kb = 0; kb < tile_kb; kb += cbs, kb_in_part += cbs) {
                     if (kb_in_part == p.kb_per_part) {
                         // hand this partial sum to the epilogue warps and restart in the other accumulator
                         umma_commit(&acc_full[acc]);
@@ -232,23 +245,26 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
                     uint64_t *ready = (THREE && !p.gather) ? &split[stage] : &full[stage];
                     if (!(ok = mbar_wait(ready, phase, abort_flag, p.status))) break;
                     tc_fence_after();
-                    const uint32_t sa = smem_u32(smem + stage * C::STAGE_BYTES);
-                    const uint32_t a_lo = smem_desc_lo(sa), b_lo = smem_desc_lo(sa + A_STAGE_BYTES);
+                    const uint32_t sa = smem_u32(smem + stage * stage_bytes);
+                    for (int c = 0; c < cbs; c++) {
+                        const uint32_t a_lo = smem_desc_lo(sa + c * A_STAGE_BYTES);
+                        const uint32_t b_lo = smem_desc_lo(sa + cbs * A_STAGE_BYTES + c * C::B_STAGE_BYTES);
 #pragma unroll
-                    for (int k = 0; k < BLOCK_K / UMMA_K; k++) {        // +32 bytes per K step = +2 in the descriptor
-                        const uint64_t da = smem_desc(a_lo + 2 * k), db = smem_desc(b_lo + 2 * k);
-                        if (THREE) {
-                            const uint64_t da_lo = smem_desc(b_lo + (C::B_STAGE_BYTES >> 4) + 2 * k);
-                            const uint64_t db_lo = smem_desc(b_lo + ((C::B_STAGE_BYTES + A_STAGE_BYTES) >> 4) + 2 * k);
-                            umma_tf32(d_tmem, da_lo, db, idesc, (kb_in_part | k) != 0);
-                            umma_tf32(d_tmem, da, db_lo, idesc, 1);
-                            umma_tf32(d_tmem, da, db, idesc, 1);
-                        } else {
-                            umma_tf32(d_tmem, da, db, idesc, (kb_in_part | k) != 0);
+                        for (int k = 0; k < BLOCK_K / UMMA_K; k++) {        // +32 bytes per K step = +2 in the descriptor
+                            const uint64_t da = smem_desc(a_lo + 2 * k), db = smem_desc(b_lo + 2 * k);
+                            if (THREE) {
+                                const uint64_t da_lo = smem_desc(b_lo + (C::B_STAGE_BYTES >> 4) + 2 * k);
+                                const uint64_t db_lo = smem_desc(b_lo + ((C::B_STAGE_BYTES + A_STAGE_BYTES) >> 4) + 2 * k);
+                                umma_tf32(d_tmem, da_lo, db, idesc, (kb_in_part | k) != 0);
+                                umma_tf32(d_tmem, da, db_lo, idesc, 1);
+                                umma_tf32(d_tmem, da, db, idesc, 1);
+                            } else {
+                                umma_tf32(d_tmem, da, db, idesc, (kb_in_part | c | k) != 0);
+                            }
                         }
                     }
                     umma_commit(&empty[stage]);     // frees the stage once these MMAs have read it
-                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                    if (++stage == stages) { stage = 0; phase ^= 1; }
                 }
                 if (ok) umma_commit(&acc_full[acc]);
                 if (++acc == 2) { acc = 0; acc_phase ^= 1; }
@@ -660,6 +676,15 @@ std::unique_ptr<TcLaunch> build_launch(nb_handle_s *h, const GemmArgs &a, bool t
     p.kb_per_part = !promote ? p.kb_per_split : (three_pass ? 1 : 16);
     p.parts = (p.kb_per_split + p.kb_per_part - 1) / p.kb_per_part;
 
+    // two K blocks per ring stage: narrow tiles (<= 128 filters) of a convolution whose channel slices pair up, a
+    // full 128-row pixel box (the second slice's tile must start on a swizzle-pattern boundary), one K split
+    p.cbs = (!three_pass && !gather && !promote && S == 1 && a.a_is_conv && block_n <= 128 && (kc % (2 * BLOCK_K)) == 0 &&
+             box.bw * box.bh * box.bn == BLOCK_M) ? 2 : 1;
+    {
+        const int stage1 = (A_STAGE_BYTES + block_n * BLOCK_K * 4) * (three_pass ? 2 : 1);
+        const int ring = std::min(8, (196 * 1024) / stage1) * stage1;       // bytes the variant's ring holds
+        p.stages = ring / (stage1 * p.cbs);
+    }
     p.gather = gather ? 1 : 0;
     if (gather) {
         p.gx = a.a;
@@ -722,7 +747,20 @@ std::unique_ptr<TcLaunch> build_launch(nb_handle_s *h, const GemmArgs &a, bool t
         if (a.lstm_h_round) check_extent(h, a.lstm_h_round, 0, fl, "rounded hidden state");
     }
 
-    if (!gather) {   // A: dims {C, W, H, N}
+    if (p.cbs == 2) {   // A: dims {32, W, H, N, C/32}; B: dims {32, N, C/32, taps}: the channel slice is a dimension of its own
+        cuuint64_t dims[5] = {(cuuint64_t)BLOCK_K, (cuuint64_t)g.W, (cuuint64_t)g.H, (cuuint64_t)g.batch, (cuuint64_t)p.c_blocks};
+        cuuint64_t strides[4] = {(cuuint64_t)g.sw * 4, (cuuint64_t)g.sh * 4, (cuuint64_t)g.sn * 4, (cuuint64_t)BLOCK_K * 4};
+        cuuint32_t bx[5] = {(cuuint32_t)BLOCK_K, (cuuint32_t)(box.bw * g.stride), (cuuint32_t)(box.bh * g.stride),
+                            (cuuint32_t)box.bn, 2};
+        cuuint32_t es[5] = {1, (cuuint32_t)g.stride, (cuuint32_t)g.stride, 1, 1};
+        encode(h, &p.tm_a, a.a, 5, dims, strides, bx, es);
+        cuuint64_t bdims[4] = {(cuuint64_t)BLOCK_K, (cuuint64_t)a.N, (cuuint64_t)p.c_blocks, (cuuint64_t)taps};
+        cuuint64_t bstrides[3] = {(cuuint64_t)a.ldb * 4, (cuuint64_t)BLOCK_K * 4, (cuuint64_t)a.ldb * 4 * (cuuint64_t)a.N};
+        cuuint32_t bbx[4] = {(cuuint32_t)BLOCK_K, (cuuint32_t)block_n, 2, 1};
+        cuuint32_t bes[4] = {1, 1, 1, 1};
+        encode(h, &p.tm_b, a.b, 4, bdims, bstrides, bbx, bes);
+    }
+    if (!gather && p.cbs == 1) {   // A: dims {C, W, H, N}
         cuuint64_t dims[4] = {(cuuint64_t)kc, (cuuint64_t)g.W, (cuuint64_t)g.H, (cuuint64_t)g.batch};
         cuuint64_t strides[3] = {(cuuint64_t)g.sw * 4, (cuuint64_t)g.sh * 4, (cuuint64_t)g.sn * 4};
         cuuint32_t bx[4] = {(cuuint32_t)BLOCK_K, (cuuint32_t)(box.bw * g.stride), (cuuint32_t)(box.bh * g.stride),
@@ -730,7 +768,7 @@ std::unique_ptr<TcLaunch> build_launch(nb_handle_s *h, const GemmArgs &a, bool t
         cuuint32_t es[4] = {1, (cuuint32_t)g.stride, (cuuint32_t)g.stride, 1};
         encode(h, &p.tm_a, a.a, 4, dims, strides, bx, es);
     }
-    {   // B: dims {Kc, N, taps}
+    if (p.cbs == 1) {   // B: dims {Kc, N, taps}
         cuuint64_t dims[3] = {(cuuint64_t)kc, (cuuint64_t)a.N, (cuuint64_t)taps};
         cuuint64_t strides[2] = {(cuuint64_t)a.ldb * 4, (cuuint64_t)a.ldb * 4 * (cuuint64_t)a.N};
         cuuint32_t bx[3] = {(cuuint32_t)BLOCK_K, (cuuint32_t)block_n, 1};
