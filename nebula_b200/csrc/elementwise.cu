@@ -192,14 +192,42 @@ __global__ void transpose_kernel(const float *src, float *dst, int rows, int col
     }
 }
 
+// 128-bit accesses when both pointers are 16-byte aligned (every buffer of the library is); scalar tail / fallback.
 __global__ void round_tf32_kernel(const float *src, float *dst, size_t n) {
-    const size_t stride = (size_t)gridDim.x * blockDim.x;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) dst[i] = round_tf32(src[i]);
+    const size_t stride = (size_t)gridDim.x * blockDim.x, tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    size_t done = 0;
+    if (((((uintptr_t)src) | ((uintptr_t)dst)) & 15) == 0) {
+        const size_t n4 = n / 4;
+        const float4 *s4 = reinterpret_cast<const float4 *>(src);
+        float4 *d4 = reinterpret_cast<float4 *>(dst);
+        for (size_t i = tid; i < n4; i += stride) {
+            float4 v = s4[i];
+            v.x = round_tf32(v.x); v.y = round_tf32(v.y); v.z = round_tf32(v.z); v.w = round_tf32(v.w);
+            d4[i] = v;
+        }
+        done = n4 * 4;
+    }
+    for (size_t i = done + tid; i < n; i += stride) dst[i] = round_tf32(src[i]);
 }
 // hi = RN_tf32(x), lo = RN_tf32(x - hi): the two terms of the 3xTF32 product.
 __global__ void split_tf32_kernel(const float *src, float *hi, float *lo, size_t n) {
-    const size_t stride = (size_t)gridDim.x * blockDim.x;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x, tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    size_t done = 0;
+    if (((((uintptr_t)src) | ((uintptr_t)hi) | ((uintptr_t)lo)) & 15) == 0) {
+        const size_t n4 = n / 4;
+        const float4 *s4 = reinterpret_cast<const float4 *>(src);
+        float4 *h4 = reinterpret_cast<float4 *>(hi), *l4 = reinterpret_cast<float4 *>(lo);
+        for (size_t i = tid; i < n4; i += stride) {
+            const float4 x = s4[i];
+            float4 h, l;
+            h.x = round_tf32(x.x); h.y = round_tf32(x.y); h.z = round_tf32(x.z); h.w = round_tf32(x.w);
+            l.x = round_tf32(x.x - h.x); l.y = round_tf32(x.y - h.y); l.z = round_tf32(x.z - h.z); l.w = round_tf32(x.w - h.w);
+            h4[i] = h;
+            l4[i] = l;
+        }
+        done = n4 * 4;
+    }
+    for (size_t i = done + tid; i < n; i += stride) {
         const float x = src[i], h = round_tf32(x);
         hi[i] = h;
         lo[i] = round_tf32(x - h);
@@ -287,6 +315,33 @@ __global__ void shortcut_kernel(const float *prev, const float *conn, float *y, 
         }
         v = apply_activation(v, act);
         y[i] = round ? round_tf32(v) : v;
+    }
+}
+
+// NHWC with both channel counts divisible by 4: one thread per 4 channels, 128-bit accesses
+__global__ void shortcut_nhwc4_kernel(const float4 *prev, const float4 *conn, float4 *y, int B, int Ci4, int Hi, int Wi, int Co4,
+                                      int Ho, int Wo, int stride, int sample, int act, int round, size_t total) {
+    const int mw = Wi < Wo ? Wi : Wo, mh = Hi < Ho ? Hi : Ho, mc = Ci4 < Co4 ? Ci4 : Co4;
+    const size_t gstride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gstride) {
+        size_t t = i;
+        const int c = (int)(t % Co4); t /= Co4;
+        const int w = (int)(t % Wo); t /= Wo;
+        const int h = (int)(t % Ho);
+        const int b = (int)(t / Ho);
+        float4 v = prev[i];
+        if (c < mc && (h % sample) == 0 && (w % sample) == 0) {
+            const int hh = h / sample, ww = w / sample;
+            const int ih = hh * stride, iw = ww * stride;
+            if (hh < mh && ww < mw && ih < Hi && iw < Wi) {
+                const float4 r = conn[(((size_t)b * Hi + ih) * Wi + iw) * Ci4 + c];
+                v.x += r.x; v.y += r.y; v.z += r.z; v.w += r.w;
+            }
+        }
+        v.x = apply_activation_fast(v.x, act); v.y = apply_activation_fast(v.y, act);
+        v.z = apply_activation_fast(v.z, act); v.w = apply_activation_fast(v.w, act);
+        if (round) { v.x = round_tf32(v.x); v.y = round_tf32(v.y); v.z = round_tf32(v.z); v.w = round_tf32(v.w); }
+        y[i] = v;
     }
 }
 
@@ -402,6 +457,31 @@ __global__ void fc_permute_kernel(const float *w, float *dst, int out, int C, in
 // -------------------------------------------------------------- split-K tail
 // y[m][n] = act(scale[n] * sum_s ws[s][m][n] + shift[n]): the epilogue of a split-K contraction
 // (slices are added in a fixed order, so the result does not depend on scheduling).
+// N % 4 == 0 (what the split-K path requires) and 16-byte aligned tensors: four columns per thread, 128-bit accesses
+__global__ void splitk_reduce4_kernel(const float4 *ws, int S, size_t MN4, int N4, const float4 *scale, const float4 *shift,
+                                      int act, int round, float4 *y) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < MN4; i += stride) {
+        float4 acc = ws[i];
+        for (int s = 1; s < S; s++) {       // slices in a fixed order: the sum does not depend on scheduling
+            const float4 v = ws[(size_t)s * MN4 + i];
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        const int n = (int)(i % N4);
+        if (scale) {
+            const float4 sc = scale[n], sh = shift[n];
+            acc.x = fmaf(acc.x, sc.x, sh.x); acc.y = fmaf(acc.y, sc.y, sh.y);
+            acc.z = fmaf(acc.z, sc.z, sh.z); acc.w = fmaf(acc.w, sc.w, sh.w);
+        } else if (shift) {
+            const float4 sh = shift[n];
+            acc.x += sh.x; acc.y += sh.y; acc.z += sh.z; acc.w += sh.w;
+        }
+        acc.x = apply_activation_fast(acc.x, act); acc.y = apply_activation_fast(acc.y, act);
+        acc.z = apply_activation_fast(acc.z, act); acc.w = apply_activation_fast(acc.w, act);
+        if (round) { acc.x = round_tf32(acc.x); acc.y = round_tf32(acc.y); acc.z = round_tf32(acc.z); acc.w = round_tf32(acc.w); }
+        y[i] = acc;
+    }
+}
 __global__ void splitk_reduce_kernel(const float *ws, int S, size_t MN, int N, const float *scale, const float *shift,
                                      int act, int round, float *y) {
     const size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -479,7 +559,7 @@ void elementwise_prepare_device() {
         (const void *)shortcut_kernel<false>, (const void *)weight_pack_kernel, (const void *)weight_rowwin_kernel,
         (const void *)rowwin_input_kernel, (const void *)weight_relayout_kernel, (const void *)fc_permute_kernel,
         (const void *)splitk_reduce_kernel, (const void *)lstm_cell_kernel, (const void *)sgemm_kernel,
-        (const void *)u8_pack_kernel};
+        (const void *)u8_pack_kernel, (const void *)splitk_reduce4_kernel, (const void *)shortcut_nhwc4_kernel};
     for (const void *k : kernels) NB_CHECK_CUDA(cudaFuncGetAttributes(&fa, k));
 }
 
@@ -582,7 +662,12 @@ void launch_shortcut(nb_handle_s *h, const nb_shortcut_desc_t &d, const float *p
     if (!total) return;
     const int stride = d.conn_width / d.out_width > 1 ? d.conn_width / d.out_width : 1;
     const int sample = d.out_width / d.conn_width > 1 ? d.out_width / d.conn_width : 1;
-    if (d.layout == NB_LAYOUT_NHWC)
+    if (d.layout == NB_LAYOUT_NHWC && (d.conn_channels % 4) == 0 && (d.out_channels % 4) == 0 &&
+        ((((uintptr_t)prev) | ((uintptr_t)conn) | ((uintptr_t)y)) & 15) == 0)
+        shortcut_nhwc4_kernel<<<grid_for(total / 4, h), TPB, 0, h->stream>>>(
+            (const float4 *)prev, (const float4 *)conn, (float4 *)y, d.batch, d.conn_channels / 4, d.conn_height, d.conn_width,
+            d.out_channels / 4, d.out_height, d.out_width, stride, sample, d.activation, round ? 1 : 0, total / 4);
+    else if (d.layout == NB_LAYOUT_NHWC)
         shortcut_kernel<true><<<grid_for(total, h), TPB, 0, h->stream>>>(
             prev, conn, y, d.batch, d.conn_channels, d.conn_height, d.conn_width, d.out_channels, d.out_height,
             d.out_width, stride, sample, d.activation, round ? 1 : 0, total);
@@ -636,7 +721,12 @@ void launch_fc_permute(nb_handle_s *h, const float *w, float *dst, int out, int 
 void launch_splitk_reduce(nb_handle_s *h, const float *ws, int S, int M, int N, const float *scale, const float *shift,
                           int act, bool round, float *y) {
     const size_t MN = (size_t)M * N;
-    splitk_reduce_kernel<<<grid_for(MN, h), TPB, 0, h->stream>>>(ws, S, MN, N, scale, shift, act, round ? 1 : 0, y);
+    const bool vec = (N % 4) == 0 && ((((uintptr_t)ws) | ((uintptr_t)y) | ((uintptr_t)scale) | ((uintptr_t)shift)) & 15) == 0;
+    if (vec)
+        splitk_reduce4_kernel<<<grid_for(MN / 4, h), TPB, 0, h->stream>>>((const float4 *)ws, S, MN / 4, N / 4, (const float4 *)scale,
+                                                                         (const float4 *)shift, act, round ? 1 : 0, (float4 *)y);
+    else
+        splitk_reduce_kernel<<<grid_for(MN, h), TPB, 0, h->stream>>>(ws, S, MN, N, scale, shift, act, round ? 1 : 0, y);
     check_launch("splitk_reduce_kernel");
     count_launch(h);
 }
