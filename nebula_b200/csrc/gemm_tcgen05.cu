@@ -76,6 +76,12 @@ struct TcParams {
     // channels fetch two 32-channel slices of a tap per request: the A map then has the slice index as a fifth
     // dimension (tm_a is 5-D, tm_b 4-D), a stage is [A0 | A1 | B0 | B1], `stages` of them fit the ring.
     int cbs, stages;
+    // Filter-column stages (col3 = 1): 3x3 stride-1 convolutions with few input channels are bound by the L2 -> shared
+    // memory traffic of re-loading the activation tile once per tap.  Here a stage is one filter COLUMN kw of one channel
+    // slice: ONE activation box of bh + 2 image rows (a_box_bytes) and the three weight tiles kh = 0..2.  Tap (kh, kw)
+    // reads the box from image row kh on: a start address kh * bw * 128 bytes further, which for bw = 16 stays on the
+    // 1024-byte repeat of the swizzle pattern.  Three activation loads per slice instead of nine.
+    int col3, a_box_bytes, stage_bytes;
     EpiParams e;                // fused epilogue
     // gather mode: warps 6-9 build the A tile in shared memory from a strided activation tensor
     // (channel counts TMA cannot address, e.g. the 3-channel input layer); rows are output pixels
@@ -111,7 +117,7 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
     // per stage: [A | B | (A_lo | B_lo)], or [A0 | A1 | B0 | B1] with two K blocks per stage
     const int cbs = THREE ? 1 : p.cbs;
     const int stages = p.stages;
-    const int stage_bytes = C::STAGE_BYTES * cbs;
+    const int stage_bytes = p.stage_bytes;
     uint8_t *out_stage = smem + STAGES * C::STAGE_BYTES;      // 2 x [128 rows][32 floats], 128B-swizzled
     uint64_t *bars = (uint64_t *)(out_stage + 2 * C::OUT_STAGE_BYTES);
     uint64_t *full = bars;                    // TMA -> (splitter or MMA)
@@ -149,7 +155,7 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
     // all 128: those rows only feed accumulator rows that are never stored, but they are given a defined value
     // (zero) once, here; no copy touches them afterwards.
     {
-        const int box_rows = p.gather ? BLOCK_M : p.bw * p.bh * p.bn;
+        const int box_rows = (p.gather || p.col3) ? BLOCK_M : p.bw * p.bh * p.bn;
         if (box_rows < BLOCK_M) {
             const int tail16 = (BLOCK_M - box_rows) * 8;          // 16-byte chunks per stage tail
             for (int i = threadIdx.x; i < stages * tail16; i += blockDim.x) {      // (two-block stages only take full boxes)
@@ -186,6 +192,23 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
                 const int kb_end = min(kb0 + p.kb_per_split, p.num_k_blocks);      // the last split may be shorter
                 int tap = kb0 / p.c_blocks, cb = kb0 - tap * p.c_blocks;
                 int kh = tap / p.ksize_w, kw = tap - kh * p.ksize_w;
+                if (!THREE && p.col3) {
+                    const uint32_t tx3 = (uint32_t)(p.a_box_bytes + 3 * C::B_STAGE_BYTES);
+                    for (int it = 0; it < 3 * p.c_blocks; it++) {       // kw fastest, then the channel slice
+                        const int cb3 = it / 3, kw3 = it - cb3 * 3;
+                        if (!(ok = mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status))) break;
+                        uint8_t *sa = smem + stage * stage_bytes;
+                        uint8_t *sb = sa + p.a_box_bytes;
+                        mbar_expect_tx(&full[stage], tx3);
+                        tma_load_4d(sa, &p.tm_a, &full[stage], cb3 * BLOCK_K, w0 + kw3, h0, n0);
+#pragma unroll
+                        for (int kh3 = 0; kh3 < 3; kh3++)
+                            tma_load_3d(sb + kh3 * C::B_STAGE_BYTES, &p.tm_b, &full[stage], cb3 * BLOCK_K, n_tile * BLOCK_N,
+                                        kh3 * 3 + kw3);
+                        if (++stage == stages) { stage = 0; phase ^= 1; }
+                    }
+                    continue;
+                }
                 const uint32_t tx_bytes = (uint32_t)(((p.gather ? 0 : p.tx_bytes_a) + C::B_STAGE_BYTES * (THREE ? 2 : 1)) * cbs);
                 for (int kb = kb0; kb < kb_end; kb += cbs) {
                     if (!(ok = mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status))) break;
@@ -231,6 +254,26 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
                 tc_fence_after();
                 uint32_t d_tmem = tmem_base + (uint32_t)(acc * BLOCK_N);
                 int kb_in_part = 0;
+                if (!THREE && p.col3) {
+                    for (int it = 0; it < 3 * p.c_blocks; it++) {
+                        if (!(ok = mbar_wait(&full[stage], phase, abort_flag, p.status))) break;
+                        tc_fence_after();
+                        const uint32_t sa = smem_u32(smem + stage * stage_bytes);
+#pragma unroll
+                        for (int kh3 = 0; kh3 < 3; kh3++) {
+                            const uint32_t a_lo = smem_desc_lo(sa + (uint32_t)(kh3 * p.bw * 128));
+                            const uint32_t b_lo = smem_desc_lo(sa + (uint32_t)p.a_box_bytes + kh3 * C::B_STAGE_BYTES);
+#pragma unroll
+                            for (int k = 0; k < BLOCK_K / UMMA_K; k++)
+                                umma_tf32(d_tmem, smem_desc(a_lo + 2 * k), smem_desc(b_lo + 2 * k), idesc, (it | kh3 | k) != 0);
+                        }
+                        umma_commit(&empty[stage]);
+                        if (++stage == stages) { stage = 0; phase ^= 1; }
+                    }
+                    if (ok) umma_commit(&acc_full[acc]);
+                    if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+                    continue;
+                }
                 const int tile_kb = min(p.kb_per_split, p.num_k_blocks - (tile % p.k_splits) * p.kb_per_split);
                 for (int kb = 0; kb < tile_kb; kb += cbs, kb_in_part += cbs) {
                     if (kb_in_part == p.kb_per_part) {
@@ -610,6 +653,12 @@ std::unique_ptr<TcLaunch> build_launch(nb_handle_s *h, const GemmArgs &a, bool t
     const int taps = g.ksize * ksize_w;
     const bool pool = a.y_pool != nullptr;
     Box box = choose_box(g.OW, g.OH, g.batch, g.stride, pool, S > 1, (double)g.sn * 4.0);
+    // filter-column stages: 3x3 / stride 1, at most 128 input channels and filters (the layers that are bound by
+    // re-loading activations from L2), a fixed 16 x 8 pixel box; not worth it when the box wastes much of the plane
+    const bool col3 = a.a_is_conv && !gather && !three_pass && S == 1 && g.ksize == 3 && ksize_w == 3 && g.stride == 1 &&
+                      g.pad <= 1 && (g.pad_w < 0 || g.pad_w == g.pad) && kc <= 128 && a.N <= 128 && g.OW >= 16 && g.OH >= 8 &&
+                      ((double)g.OW / ((g.OW + 15) / 16 * 16)) * ((double)g.OH / ((g.OH + 7) / 8 * 8)) >= 0.8;
+    if (col3) box = Box{16, 8, 1};
     p.bw = box.bw; p.bh = box.bh; p.bn = box.bn;
     p.tiles_w = (g.OW + box.bw - 1) / box.bw;
     p.tiles_h = (g.OH + box.bh - 1) / box.bh;
@@ -678,12 +727,16 @@ std::unique_ptr<TcLaunch> build_launch(nb_handle_s *h, const GemmArgs &a, bool t
 
     // two K blocks per ring stage: narrow tiles (<= 128 filters) of a convolution whose channel slices pair up, a
     // full 128-row pixel box (the second slice's tile must start on a swizzle-pattern boundary), one K split
-    p.cbs = (!three_pass && !gather && !promote && S == 1 && a.a_is_conv && block_n <= 128 && (kc % (2 * BLOCK_K)) == 0 &&
-             box.bw * box.bh * box.bn == BLOCK_M) ? 2 : 1;
+    p.col3 = (col3 && !promote && block_n <= 128) ? 1 : 0;
+    p.cbs = (!p.col3 && !three_pass && !gather && !promote && S == 1 && a.a_is_conv && block_n <= 128 &&
+             (kc % (2 * BLOCK_K)) == 0 && box.bw * box.bh * box.bn == BLOCK_M) ? 2 : 1;
     {
-        const int stage1 = (A_STAGE_BYTES + block_n * BLOCK_K * 4) * (three_pass ? 2 : 1);
+        const int b_stage = block_n * BLOCK_K * 4;
+        const int stage1 = (A_STAGE_BYTES + b_stage) * (three_pass ? 2 : 1);
         const int ring = std::min(8, (196 * 1024) / stage1) * stage1;       // bytes the variant's ring holds
-        p.stages = ring / (stage1 * p.cbs);
+        p.a_box_bytes = BLOCK_K * 4 * box.bw * (box.bh + 2);
+        p.stage_bytes = p.col3 ? p.a_box_bytes + 3 * b_stage : stage1 * p.cbs;
+        p.stages = std::min(8, ring / p.stage_bytes);
     }
     p.gather = gather ? 1 : 0;
     if (gather) {
@@ -763,8 +816,8 @@ std::unique_ptr<TcLaunch> build_launch(nb_handle_s *h, const GemmArgs &a, bool t
     if (!gather && p.cbs == 1) {   // A: dims {C, W, H, N}
         cuuint64_t dims[4] = {(cuuint64_t)kc, (cuuint64_t)g.W, (cuuint64_t)g.H, (cuuint64_t)g.batch};
         cuuint64_t strides[3] = {(cuuint64_t)g.sw * 4, (cuuint64_t)g.sh * 4, (cuuint64_t)g.sn * 4};
-        cuuint32_t bx[4] = {(cuuint32_t)BLOCK_K, (cuuint32_t)(box.bw * g.stride), (cuuint32_t)(box.bh * g.stride),
-                            (cuuint32_t)box.bn};
+        cuuint32_t bx[4] = {(cuuint32_t)BLOCK_K, (cuuint32_t)(box.bw * g.stride),
+                            (cuuint32_t)(p.col3 ? box.bh + 2 : box.bh * g.stride), (cuuint32_t)box.bn};
         cuuint32_t es[4] = {1, (cuuint32_t)g.stride, (cuuint32_t)g.stride, 1};
         encode(h, &p.tm_a, a.a, 4, dims, strides, bx, es);
     }
@@ -805,7 +858,8 @@ std::unique_ptr<TcLaunch> build_launch(nb_handle_s *h, const GemmArgs &a, bool t
               std::to_string(taps) + " stride=" + std::to_string(g.stride) + " out=" + std::to_string(g.OW) + "x" +
               std::to_string(g.OH) + "x" + std::to_string(g.batch) + " box=" + std::to_string(box.bw) + "x" +
               std::to_string(box.bh) + "x" + std::to_string(box.bn) + " block_n=" + std::to_string(block_n) +
-              " splits=" + std::to_string(S) + (gather ? " gather" : "") + (three_pass ? " 3xtf32" : "") +
+              " splits=" + std::to_string(S) + (p.col3 ? " col3" : "") + (p.cbs == 2 ? " cbs2" : "") + (gather ? " gather" : "") +
+              (three_pass ? " 3xtf32" : "") +
               (pool ? " pool" : "") + (a.addend ? " addend" : "") + (a.lstm_H ? " lstm" : "") + "]";
     return L;
 }

@@ -4,6 +4,7 @@
     python -m nebula_b200.microbench fc --batch 256 --inputs 25088 --outputs 4096
     python -m nebula_b200.microbench lstm --batch 64 --inputs 1024 --outputs 1024 --steps 128
     python -m nebula_b200.microbench sweep        # the single-convolution sweep (batch 64, stride 1)
+    python -m nebula_b200.microbench vgg_layers --batch 64    # a VGG-16 pass through the per-layer NCHW entries
 
 Prints one JSON line per case: device time per call (CUDA events on the stream
 the kernels run on), algorithmic TFLOP/s and GB/s.
@@ -92,12 +93,72 @@ def bench_lstm(h, batch, inputs, hidden, steps, math, iters=10, warmup=3):
                 us_per_step=round(ms * 1e3 / steps, 2), tflops=round(flops / ms / 1e9, 1))
 
 
+def bench_vgg_per_layer(h, batch, math, iters=5, warmup=2):
+    """One VGG-16 forward pass driven layer by layer through the per-layer entry points with the reference's own
+    NCHW buffers (what a Nebula build bound as in INTEGRATION.md sections 2-4 executes), next to the network
+    executor's pass over the same cfg."""
+    import numpy as np
+    from . import workloads
+    h.set_math(math)
+    wl = workloads.vgg16(batch=batch)
+    w = wl.make_weights(1)
+    x = torch.from_numpy(wl.make_input(2)).cuda()
+    pos, c, hw = 0, 3, 224
+    convs, fcs = [], []
+    for width, reps in zip((64, 128, 256, 512, 512), (2, 2, 3, 3, 3)):
+        for _ in range(reps):
+            plan = api.Conv2d(h, batch, c, hw, hw, width, 3, 1, 1, False, "relu", api.LAYOUT_NCHW)
+            nb, nw = width, width * c * 9
+            plan.set_weights(np.ascontiguousarray(w[pos + nb:pos + nb + nw]), np.ascontiguousarray(w[pos:pos + nb]))
+            plan.prepare()
+            pos += nb + nw
+            convs.append((plan, reps))
+            c = width
+        hw //= 2
+    inp = 512 * 7 * 7
+    for out, act in ((4096, "relu"), (4096, "relu"), (1000, "linear")):
+        plan = api.Connected(h, batch, inp, out, False, act)
+        plan.set_weights(np.ascontiguousarray(w[pos + out:pos + out + out * inp]), np.ascontiguousarray(w[pos:pos + out]))
+        plan.prepare()
+        pos += out + out * inp
+        fcs.append(plan)
+        inp = out
+
+    def run():
+        t, i = x, 0
+        for reps in (2, 2, 3, 3, 3):
+            for _ in range(reps):
+                t = convs[i][0].forward(t)
+                i += 1
+            t = h.pool(t, 2, 2, 0, "max", api.LAYOUT_NCHW)
+        t = t.reshape(batch, -1)
+        for p in fcs:
+            t = p.forward(t)
+        return h.softmax(t)
+
+    ms_layers = _time(run, iters, warmup)
+    net = api.Network(h, wl.cfg)
+    net.load_weights(w)
+    ms_net = _time(lambda: net.forward(x), iters, warmup)
+    h.synchronize()
+    probs = run().cpu().numpy()
+    same = bool(np.array_equal(probs, net.output().reshape(batch, -1))) if True else None
+    net.close()
+    for p, _ in convs:
+        p.close()
+    for p in fcs:
+        p.close()
+    return dict(op="vgg16 layer by layer (NCHW entry points)", batch=batch, math=math, ms=round(ms_layers, 3),
+                images_per_s=round(batch / ms_layers * 1e3, 1), executor_ms=round(ms_net, 3),
+                executor_images_per_s=round(batch / ms_net * 1e3, 1), identical_probabilities=same)
+
+
 SWEEP = [(256, 56, 256, 3, 1), (512, 14, 512, 3, 1), (64, 56, 256, 1, 0)]
 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["conv", "fc", "lstm", "sweep", "vgg"])
+    ap.add_argument("op", choices=["conv", "fc", "lstm", "sweep", "vgg", "vgg_layers"])
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--channels", type=int, default=256)
     ap.add_argument("--size", type=int, default=56)
@@ -119,6 +180,8 @@ def main():
         print(json.dumps(bench_fc(h, a.batch, a.inputs, a.outputs, a.math, a.iters, a.warmup)))
     elif a.op == "lstm":
         print(json.dumps(bench_lstm(h, a.batch, a.inputs, a.outputs, a.steps, a.math, a.iters, a.warmup)))
+    elif a.op == "vgg_layers":
+        print(json.dumps(bench_vgg_per_layer(h, a.batch, a.math, a.iters, a.warmup)))
     elif a.op == "sweep":
         for c, s, f, k, p in SWEEP:
             print(json.dumps(bench_conv(h, a.batch, c, s, f, k, 1, p, a.math, a.iters, a.warmup)), flush=True)
