@@ -142,7 +142,9 @@ def bench_vgg_per_layer(h, batch, math, iters=5, warmup=2):
     ms_net = _time(lambda: net.forward(x), iters, warmup)
     h.synchronize()
     probs = run().cpu().numpy()
-    same = bool(np.array_equal(probs, net.output().reshape(batch, -1))) if True else None
+    # (not bit-identical: the executor feeds the first connected layer an NHWC tensor through permuted weight columns,
+    # so its products are summed in another order)
+    diff = float(np.abs(probs - net.output().reshape(batch, -1)).max())
     net.close()
     for p, _ in convs:
         p.close()
@@ -150,7 +152,7 @@ def bench_vgg_per_layer(h, batch, math, iters=5, warmup=2):
         p.close()
     return dict(op="vgg16 layer by layer (NCHW entry points)", batch=batch, math=math, ms=round(ms_layers, 3),
                 images_per_s=round(batch / ms_layers * 1e3, 1), executor_ms=round(ms_net, 3),
-                executor_images_per_s=round(batch / ms_net * 1e3, 1), identical_probabilities=same)
+                executor_images_per_s=round(batch / ms_net * 1e3, 1), max_abs_diff_of_probabilities=diff)
 
 
 SWEEP = [(256, 56, 256, 3, 1), (512, 14, 512, 3, 1), (64, 56, 256, 1, 0)]
