@@ -82,6 +82,10 @@ struct TcParams {
     // reads the box from image row kh on: a start address kh * bw * 128 bytes further, which for bw = 16 stays on the
     // 1024-byte repeat of the swizzle pattern.  Three activation loads per slice instead of nine.
     int col3, a_box_bytes, stage_bytes;
+    // col3 only: a tile of `halves` (1 or 2) vertically adjacent 16 x 8 boxes.  Both read the same activation box
+    // (bh * halves + 2 image rows, the second half 8 image rows further down) and the same three weight tiles, which
+    // halves the weight traffic per pixel; each half has its own accumulator columns.
+    int halves;
     EpiParams e;                // fused epilogue
     // gather mode: warps 6-9 build the A tile in shared memory from a strided activation tensor
     // (channel counts TMA cannot address, e.g. the 3-channel input layer); rows are output pixels
@@ -118,6 +122,9 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
     const int cbs = THREE ? 1 : p.cbs;
     const int stages = p.stages;
     const int stage_bytes = p.stage_bytes;
+    const int halves = (THREE || PROMOTE || BLOCK_N > 128) ? 1 : p.halves;
+    const int acc_cols = halves * BLOCK_N;              // TMEM columns of one accumulator set
+    const uint32_t tmem_cols = (uint32_t)(C::TMEM_COLS * halves);
     uint8_t *out_stage = smem + STAGES * C::STAGE_BYTES;      // 2 x [128 rows][32 floats], 128B-swizzled
     uint64_t *bars = (uint64_t *)(out_stage + 2 * C::OUT_STAGE_BYTES);
     uint64_t *full = bars;                    // TMA -> (splitter or MMA)
@@ -147,7 +154,7 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
-                     "r"((uint32_t)C::TMEM_COLS)
+                     "r"(tmem_cols)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -186,7 +193,7 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
                 const int th = (m_tile / p.tiles_w) % p.tiles_h;
                 const int tn = m_tile / (p.tiles_w * p.tiles_h);
                 const int w0 = tw * p.bw * p.stride - p.pad_w;
-                const int h0 = th * p.bh * p.stride - p.pad_h;
+                const int h0 = th * p.bh * halves * p.stride - p.pad_h;
                 const int n0 = tn * p.bn;
                 const int kb0 = split * p.kb_per_split;
                 const int kb_end = min(kb0 + p.kb_per_split, p.num_k_blocks);      // the last split may be shorter
@@ -252,7 +259,7 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
                 if (!(ok = mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag, p.status))) break;
                 tc_fence_after();
-                uint32_t d_tmem = tmem_base + (uint32_t)(acc * BLOCK_N);
+                uint32_t d_tmem = tmem_base + (uint32_t)(acc * acc_cols);
                 int kb_in_part = 0;
                 if (!THREE && p.col3) {
                     for (int it = 0; it < 3 * p.c_blocks; it++) {
@@ -261,11 +268,14 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
                         const uint32_t sa = smem_u32(smem + stage * stage_bytes);
 #pragma unroll
                         for (int kh3 = 0; kh3 < 3; kh3++) {
-                            const uint32_t a_lo = smem_desc_lo(sa + (uint32_t)(kh3 * p.bw * 128));
                             const uint32_t b_lo = smem_desc_lo(sa + (uint32_t)p.a_box_bytes + kh3 * C::B_STAGE_BYTES);
+                            for (int hf = 0; hf < halves; hf++) {       // image row kh3 (+ bh for the second half) of the box
+                                const uint32_t a_lo = smem_desc_lo(sa + (uint32_t)((hf * p.bh + kh3) * p.bw * 128));
 #pragma unroll
-                            for (int k = 0; k < BLOCK_K / UMMA_K; k++)
-                                umma_tf32(d_tmem, smem_desc(a_lo + 2 * k), smem_desc(b_lo + 2 * k), idesc, (it | kh3 | k) != 0);
+                                for (int k = 0; k < BLOCK_K / UMMA_K; k++)
+                                    umma_tf32(d_tmem + (uint32_t)(hf * BLOCK_N), smem_desc(a_lo + 2 * k), smem_desc(b_lo + 2 * k),
+                                              idesc, (it | kh3 | k) != 0);
+                            }
                         }
                         umma_commit(&empty[stage]);
                         if (++stage == stages) { stage = 0; phase ^= 1; }
@@ -282,7 +292,7 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
                         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
                         if (!(ok = mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag, p.status))) break;
                         tc_fence_after();
-                        d_tmem = tmem_base + (uint32_t)(acc * BLOCK_N);
+                        d_tmem = tmem_base + (uint32_t)(acc * acc_cols);
                         kb_in_part = 0;
                     }
                     uint64_t *ready = (THREE && !p.gather) ? &split[stage] : &full[stage];
@@ -339,22 +349,35 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
             const int tw = m_tile % p.tiles_w;
             const int th = (m_tile / p.tiles_w) % p.tiles_h;
             const int tn = m_tile / (p.tiles_w * p.tiles_h);
-            const int ow = tw * p.bw + rw, oh = th * p.bh + rh, n = tn * p.bn + rn;
+            const int ow = tw * p.bw + rw, oh = th * p.bh * halves + rh, n = tn * p.bn + rn;
             const bool row_ok = (rn < p.bn) && ow < p.OW && oh < p.OH && n < p.NB;
             const long row = ((long)n * p.OH + oh) * p.OW + ow;
             const EpiRow erow{r, row, row_ok, addend_row(p.e, row_ok, row, n, oh, ow)};
-            const EpiBox ebox{p.bw, p.bh, p.bn, tw * p.bw, th * p.bh, tn * p.bn + split * p.NB};
+            const EpiBox ebox{p.bw, p.bh, p.bn, tw * p.bw, th * p.bh * halves, tn * p.bn + split * p.NB};
             if (!PROMOTE || p.parts == 1) {
                 if (!(ok = epilogue_all(mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status), bar_id))) break;
                 tc_fence_after();
 #pragma unroll 1
-                for (int chunk = grp; chunk < BLOCK_N / 32; chunk += 2) {
-                    const int col0 = n_tile * BLOCK_N + chunk * 32;
-                    if (col0 >= p.e.N) break;         // uniform across the group
-                    uint32_t v[32];
-                    tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BLOCK_N + chunk * 32), v);
-                    tmem_ld_wait();
-                    epilogue_chunk(p.e, &p.tm_y, &p.tm_yp, v, col0, erow, ebox, slab, bar_id, store_thread, t);
+                for (int hf = 0; hf < halves; hf++) {
+                    // the second half of a two-box tile: the same raster p.bh image rows further down
+                    EpiRow hrow = erow;
+                    EpiBox hbox = ebox;
+                    if (hf) {
+                        const int oh2 = oh + p.bh;
+                        hrow.row_ok = (rn < p.bn) && ow < p.OW && oh2 < p.OH && n < p.NB;
+                        hrow.grow = ((long)n * p.OH + oh2) * p.OW + ow;
+                        hrow.arow = addend_row(p.e, hrow.row_ok, hrow.grow, n, oh2, ow);
+                        hbox.oh0 += p.bh;
+                    }
+#pragma unroll 1
+                    for (int chunk = grp; chunk < BLOCK_N / 32; chunk += 2) {
+                        const int col0 = n_tile * BLOCK_N + chunk * 32;
+                        if (col0 >= p.e.N) break;         // uniform across the group
+                        uint32_t v[32];
+                        tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * acc_cols + hf * BLOCK_N + chunk * 32), v);
+                        tmem_ld_wait();
+                        epilogue_chunk(p.e, &p.tm_y, &p.tm_yp, v, col0, hrow, hbox, slab, bar_id, store_thread, t);
+                    }
                 }
                 tc_fence_before();
                 mbar_arrive(&acc_empty[acc]);
@@ -505,9 +528,7 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
     if (warp == 1) {
         __syncwarp();
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
-                     "r"((uint32_t)C::TMEM_COLS)
-                     : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
     }
 }
 
@@ -659,9 +680,12 @@ std::unique_ptr<TcLaunch> build_launch(nb_handle_s *h, const GemmArgs &a, bool t
                       g.pad <= 1 && (g.pad_w < 0 || g.pad_w == g.pad) && kc <= 128 && a.N <= 128 && g.OW >= 16 && g.OH >= 8 &&
                       ((double)g.OW / ((g.OW + 15) / 16 * 16)) * ((double)g.OH / ((g.OH + 7) / 8 * 8)) >= 0.8;
     if (col3) box = Box{16, 8, 1};
+    // two boxes per tile when the plane is tall enough for 16-row tiles not to waste much of it
+    const int halves = (col3 && g.OH >= 16 && ((double)g.OW / ((g.OW + 15) / 16 * 16)) * ((double)g.OH / ((g.OH + 15) / 16 * 16)) >= 0.8)
+                           ? 2 : 1;
     p.bw = box.bw; p.bh = box.bh; p.bn = box.bn;
     p.tiles_w = (g.OW + box.bw - 1) / box.bw;
-    p.tiles_h = (g.OH + box.bh - 1) / box.bh;
+    p.tiles_h = (g.OH + box.bh * halves - 1) / (box.bh * halves);
     p.tiles_n = (g.batch + box.bn - 1) / box.bn;
     p.OW = g.OW; p.OH = g.OH; p.NB = g.batch;
     p.ksize_w = ksize_w; p.stride = g.stride; p.pad_h = g.pad; p.pad_w = g.pad_w >= 0 ? g.pad_w : g.pad;
@@ -728,13 +752,15 @@ std::unique_ptr<TcLaunch> build_launch(nb_handle_s *h, const GemmArgs &a, bool t
     // two K blocks per ring stage: narrow tiles (<= 128 filters) of a convolution whose channel slices pair up, a
     // full 128-row pixel box (the second slice's tile must start on a swizzle-pattern boundary), one K split
     p.col3 = (col3 && !promote && block_n <= 128) ? 1 : 0;
+    p.halves = p.col3 ? halves : 1;
+    if (halves == 2 && !p.col3) throw Error(NB_ERR_UNSUPPORTED, "two-box tiles need the filter-column mode");
     p.cbs = (!p.col3 && !three_pass && !gather && !promote && S == 1 && a.a_is_conv && block_n <= 128 &&
              (kc % (2 * BLOCK_K)) == 0 && box.bw * box.bh * box.bn == BLOCK_M) ? 2 : 1;
     {
         const int b_stage = block_n * BLOCK_K * 4;
         const int stage1 = (A_STAGE_BYTES + b_stage) * (three_pass ? 2 : 1);
         const int ring = std::min(8, (196 * 1024) / stage1) * stage1;       // bytes the variant's ring holds
-        p.a_box_bytes = BLOCK_K * 4 * box.bw * (box.bh + 2);
+        p.a_box_bytes = BLOCK_K * 4 * box.bw * (box.bh * halves + 2);
         p.stage_bytes = p.col3 ? p.a_box_bytes + 3 * b_stage : stage1 * p.cbs;
         p.stages = std::min(8, ring / p.stage_bytes);
     }
@@ -769,7 +795,8 @@ std::unique_ptr<TcLaunch> build_launch(nb_handle_s *h, const GemmArgs &a, bool t
     } else {
         const long long wmin = -(long long)p.pad_w, hmin = -(long long)p.pad_h;
         const long long wmax = (long long)(p.tiles_w - 1) * box.bw * g.stride + wmin + (ksize_w - 1) + (long long)box.bw * g.stride - 1;
-        const long long hmax = (long long)(p.tiles_h - 1) * box.bh * g.stride + hmin + (g.ksize - 1) + (long long)box.bh * g.stride - 1;
+        const long long bh_tile = (long long)box.bh * halves;
+        const long long hmax = (long long)(p.tiles_h - 1) * bh_tile * g.stride + hmin + (g.ksize - 1) + bh_tile * g.stride - 1;
         const long long nmax = (long long)p.tiles_n * box.bn - 1;
         const long long lo = std::min(wmin, 0LL) * g.sw + std::min(hmin, 0LL) * g.sh;
         const long long hi = wmax * g.sw + hmax * g.sh + nmax * g.sn + cmax + 1;
@@ -817,7 +844,7 @@ std::unique_ptr<TcLaunch> build_launch(nb_handle_s *h, const GemmArgs &a, bool t
         cuuint64_t dims[4] = {(cuuint64_t)kc, (cuuint64_t)g.W, (cuuint64_t)g.H, (cuuint64_t)g.batch};
         cuuint64_t strides[3] = {(cuuint64_t)g.sw * 4, (cuuint64_t)g.sh * 4, (cuuint64_t)g.sn * 4};
         cuuint32_t bx[4] = {(cuuint32_t)BLOCK_K, (cuuint32_t)(box.bw * g.stride),
-                            (cuuint32_t)(p.col3 ? box.bh + 2 : box.bh * g.stride), (cuuint32_t)box.bn};
+                            (cuuint32_t)(p.col3 ? box.bh * halves + 2 : box.bh * g.stride), (cuuint32_t)box.bn};
         cuuint32_t es[4] = {1, (cuuint32_t)g.stride, (cuuint32_t)g.stride, 1};
         encode(h, &p.tm_a, a.a, 4, dims, strides, bx, es);
     }
@@ -858,7 +885,7 @@ std::unique_ptr<TcLaunch> build_launch(nb_handle_s *h, const GemmArgs &a, bool t
               std::to_string(taps) + " stride=" + std::to_string(g.stride) + " out=" + std::to_string(g.OW) + "x" +
               std::to_string(g.OH) + "x" + std::to_string(g.batch) + " box=" + std::to_string(box.bw) + "x" +
               std::to_string(box.bh) + "x" + std::to_string(box.bn) + " block_n=" + std::to_string(block_n) +
-              " splits=" + std::to_string(S) + (p.col3 ? " col3" : "") + (p.cbs == 2 ? " cbs2" : "") + (gather ? " gather" : "") +
+              " splits=" + std::to_string(S) + (p.col3 ? (p.halves == 2 ? " col3x2" : " col3") : "") + (p.cbs == 2 ? " cbs2" : "") + (gather ? " gather" : "") +
               (three_pass ? " 3xtf32" : "") +
               (pool ? " pool" : "") + (a.addend ? " addend" : "") + (a.lstm_H ? " lstm" : "") + "]";
     return L;
