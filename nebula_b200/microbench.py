@@ -5,6 +5,7 @@
     python -m nebula_b200.microbench lstm --batch 64 --inputs 1024 --outputs 1024 --steps 128
     python -m nebula_b200.microbench sweep        # the single-convolution sweep (batch 64, stride 1)
     python -m nebula_b200.microbench vgg_layers --batch 64    # a VGG-16 pass through the per-layer NCHW entries
+    python -m nebula_b200.microbench passes --workload vgg16 --batch 256 --passes 2   # whole passes (for a profiler)
 
 Prints one JSON line per case: device time per call (CUDA events on the stream
 the kernels run on), algorithmic TFLOP/s and GB/s.
@@ -155,12 +156,32 @@ def bench_vgg_per_layer(h, batch, math, iters=5, warmup=2):
                 executor_images_per_s=round(batch / ms_net * 1e3, 1), max_abs_diff_of_probabilities=diff)
 
 
+def run_passes(h, workload, batch, math, passes):
+    """`passes` forward passes of a benchmark network through the executor (the thing to put under a profiler)."""
+    from . import workloads
+    h.set_math(math)
+    wl = workloads.WORKLOADS[workload](batch=batch)
+    net = api.Network(h, wl.cfg)
+    net.load_weights(wl.make_weights(1))
+    x = torch.from_numpy(wl.make_input(2)).cuda()
+    torch.cuda.synchronize()
+    n0 = h.launch_count()
+    ms = _time(lambda: net.forward(x), passes, 0)
+    h.synchronize()
+    out = dict(op="passes", workload=workload, batch=batch, math=math, passes=passes, ms_per_pass=round(ms, 4),
+               launches_per_pass=(h.launch_count() - n0) // passes, launches_before=n0)
+    net.close()
+    return out
+
+
 SWEEP = [(256, 56, 256, 3, 1), (512, 14, 512, 3, 1), (64, 56, 256, 1, 0)]
 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["conv", "fc", "lstm", "sweep", "vgg", "vgg_layers"])
+    ap.add_argument("op", choices=["conv", "fc", "lstm", "sweep", "vgg", "vgg_layers", "passes"])
+    ap.add_argument("--workload", default="vgg16")
+    ap.add_argument("--passes", type=int, default=2)
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--channels", type=int, default=256)
     ap.add_argument("--size", type=int, default=56)
@@ -182,6 +203,8 @@ def main():
         print(json.dumps(bench_fc(h, a.batch, a.inputs, a.outputs, a.math, a.iters, a.warmup)))
     elif a.op == "lstm":
         print(json.dumps(bench_lstm(h, a.batch, a.inputs, a.outputs, a.steps, a.math, a.iters, a.warmup)))
+    elif a.op == "passes":
+        print(json.dumps(run_passes(h, a.workload, a.batch, a.math, a.passes)))
     elif a.op == "vgg_layers":
         print(json.dumps(bench_vgg_per_layer(h, a.batch, a.math, a.iters, a.warmup)))
     elif a.op == "sweep":
