@@ -99,20 +99,64 @@ struct TcParams {
     int *status;
 };
 
+// The digits (split, n_tile, tw, th, tn) of a CTA's current tile.  Decoding a tile index costs seven integer
+// divisions (over a thousand cycles of dependent instructions on a role's critical path), so the index is decoded
+// once and then advanced by the digits of the grid stride, with carries.
+struct TileIter {
+    int split, n_tile, tw, th, tn;      // current tile
+    int ds, dn, dw, dh, dt;             // the grid stride
+
+    __device__ __forceinline__ static void decode(const TcParams &p, int tile, int &s, int &n, int &w, int &h, int &t) {
+        s = tile % p.k_splits;
+        const int mn = tile / p.k_splits;
+        const int m_tile = p.m_fastest ? mn % p.m_tiles : mn / p.n_tiles;
+        n = p.m_fastest ? mn / p.m_tiles : mn % p.n_tiles;
+        w = m_tile % p.tiles_w;
+        h = (m_tile / p.tiles_w) % p.tiles_h;
+        t = m_tile / (p.tiles_w * p.tiles_h);
+    }
+    __device__ __forceinline__ TileIter(const TcParams &p, int first, int step) {
+        decode(p, first, split, n_tile, tw, th, tn);
+        decode(p, step, ds, dn, dw, dh, dt);
+    }
+    // digit + stride digit + carry < 2 * radix: one conditional subtraction per digit
+    __device__ __forceinline__ static int add(int &digit, int inc, int radix) {
+        digit += inc;
+        const int carry = digit >= radix ? 1 : 0;
+        if (carry) digit -= radix;
+        return carry;
+    }
+    __device__ __forceinline__ void next(const TcParams &p) {
+        int c = add(split, ds, p.k_splits);
+        if (p.m_fastest) {
+            c = add(tw, dw + c, p.tiles_w);
+            c = add(th, dh + c, p.tiles_h);
+            c = add(tn, dt + c, p.tiles_n);
+            n_tile += dn + c;
+        } else {
+            c = add(n_tile, dn + c, p.n_tiles);
+            c = add(tw, dw + c, p.tiles_w);
+            c = add(th, dh + c, p.tiles_h);
+            tn += dt + c;
+        }
+    }
+};
+
 template <int BLOCK_N, bool THREE>
 struct Cfg {
     static constexpr int B_STAGE_BYTES = BLOCK_N * BLOCK_K * 4;
     static constexpr int STAGE_BYTES = (A_STAGE_BYTES + B_STAGE_BYTES) * (THREE ? 2 : 1);
     static constexpr int STAGES = (196 * 1024) / STAGE_BYTES < 8 ? (196 * 1024) / STAGE_BYTES : 8;
     static constexpr int TMEM_COLS = 2 * BLOCK_N;
-    static constexpr int MAX_THREADS = (BLOCK_N == 256 && !THREE) ? 320 : 448;   // 256-wide tiles never run the extra operand warps
     static constexpr int OUT_STAGE_BYTES = BLOCK_M * 32 * 4;     // one 128 x 32 output slab
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 2 * OUT_STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
 };
 
 // ------------------------------------------------------------------- kernel
-template <int BLOCK_N, bool THREE, bool PROMOTE>
-__global__ void __launch_bounds__(Cfg<BLOCK_N, THREE>::MAX_THREADS, 1)
+// GATHER: warps 10-13 build the A tile (compiled apart so that the common variants, which launch ten warps, are not
+// held to the register budget of fourteen).
+template <int BLOCK_N, bool THREE, bool PROMOTE, bool GATHER>
+__global__ void __launch_bounds__((THREE || GATHER) ? 448 : 320, 1)
 gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
     using C = Cfg<BLOCK_N, THREE>;
     constexpr int STAGES = C::STAGES;                   // barrier slots; the ring uses the first p.stages of them
@@ -141,7 +185,7 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
-            mbar_init(&full[s], p.gather ? 129 : 1);
+            mbar_init(&full[s], GATHER ? 129 : 1);
             mbar_init(&empty[s], 1);
             mbar_init(&split[s], 128);
         }
@@ -162,7 +206,7 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
     // all 128: those rows only feed accumulator rows that are never stored, but they are given a defined value
     // (zero) once, here; no copy touches them afterwards.
     {
-        const int box_rows = (p.gather || p.col3) ? BLOCK_M : p.bw * p.bh * p.bn;
+        const int box_rows = (GATHER || p.col3) ? BLOCK_M : p.bw * p.bh * p.bn;
         if (box_rows < BLOCK_M) {
             const int tail16 = (BLOCK_M - box_rows) * 8;          // 16-byte chunks per stage tail
             for (int i = threadIdx.x; i < stages * tail16; i += blockDim.x) {      // (two-block stages only take full boxes)
@@ -179,93 +223,102 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
 
     if (warp == 0) {
         // ------------------------------------------------------ TMA producer
-        // One thread issues every copy.  Its loop is the floor under the K-block rate of narrow tiles (a few hundred
-        // cycles per issued copy), so the K-block coordinates advance by increments instead of divisions.
-        if (elect_one()) {
-            int stage = 0;
-            uint32_t phase = 0;
-            bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const int split = tile % p.k_splits, mn = tile / p.k_splits;
-                const int m_tile = p.m_fastest ? mn % p.m_tiles : mn / p.n_tiles;
-                const int n_tile = p.m_fastest ? mn / p.m_tiles : mn % p.n_tiles;
-                const int tw = m_tile % p.tiles_w;
-                const int th = (m_tile / p.tiles_w) % p.tiles_h;
-                const int tn = m_tile / (p.tiles_w * p.tiles_h);
-                const int w0 = tw * p.bw * p.stride - p.pad_w;
-                const int h0 = th * p.bh * halves * p.stride - p.pad_h;
-                const int n0 = tn * p.bn;
-                const int kb0 = split * p.kb_per_split;
-                const int kb_end = min(kb0 + p.kb_per_split, p.num_k_blocks);      // the last split may be shorter
-                int tap = kb0 / p.c_blocks, cb = kb0 - tap * p.c_blocks;
-                int kh = tap / p.ksize_w, kw = tap - kh * p.ksize_w;
-                if (!THREE && p.col3) {
-                    const uint32_t tx3 = (uint32_t)(p.a_box_bytes + 3 * C::B_STAGE_BYTES);
-                    for (int it = 0; it < 3 * p.c_blocks; it++) {       // kw fastest, then the channel slice
-                        const int cb3 = it / 3, kw3 = it - cb3 * 3;
+        // One elected lane runs the loop and issues every copy.  (Measured: running the loop and the waits in all 32 lanes
+        // with only the copies elected -- uniform control flow -- changes nothing for narrow tiles and costs 256-wide
+        // tiles 2 %.)
+        const bool leader = elect_one();
+        if (leader) {
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        TileIter ti(p, blockIdx.x, gridDim.x);
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ti.next(p)) {
+            const int split = ti.split, n_tile = ti.n_tile, tw = ti.tw, th = ti.th, tn = ti.tn;
+            const int w0 = tw * p.bw * p.stride - p.pad_w;
+            const int h0 = th * p.bh * halves * p.stride - p.pad_h;
+            const int n0 = tn * p.bn;
+            const int kb0 = split * p.kb_per_split;
+            const int kb_end = min(kb0 + p.kb_per_split, p.num_k_blocks);      // the last split may be shorter
+            if (!THREE && p.col3) {
+                // two requests per stage: the activation box and the three weight tiles of this filter column
+                // (tm_b is 4-D here, {C, N, kw, kh}: a box of one kw and all three kh)
+                const uint32_t tx3 = (uint32_t)(p.a_box_bytes + 3 * C::B_STAGE_BYTES);
+                for (int cb3 = 0; cb3 < p.c_blocks && ok; cb3++) {       // kw fastest, then the channel slice
+                    for (int kw3 = 0; kw3 < 3; kw3++) {
                         if (!(ok = mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status))) break;
                         uint8_t *sa = smem + stage * stage_bytes;
-                        uint8_t *sb = sa + p.a_box_bytes;
-                        mbar_expect_tx(&full[stage], tx3);
-                        tma_load_4d(sa, &p.tm_a, &full[stage], cb3 * BLOCK_K, w0 + kw3, h0, n0);
-#pragma unroll
-                        for (int kh3 = 0; kh3 < 3; kh3++)
-                            tma_load_3d(sb + kh3 * C::B_STAGE_BYTES, &p.tm_b, &full[stage], cb3 * BLOCK_K, n_tile * BLOCK_N,
-                                        kh3 * 3 + kw3);
+                        if (leader) {
+                            mbar_expect_tx(&full[stage], tx3);
+                            tma_load_4d(sa, &p.tm_a, &full[stage], cb3 * BLOCK_K, w0 + kw3, h0, n0);
+                            tma_load_4d(sa + p.a_box_bytes, &p.tm_b, &full[stage], cb3 * BLOCK_K, n_tile * BLOCK_N, kw3, 0);
+                        }
                         if (++stage == stages) { stage = 0; phase ^= 1; }
                     }
-                    continue;
                 }
-                const uint32_t tx_bytes = (uint32_t)(((p.gather ? 0 : p.tx_bytes_a) + C::B_STAGE_BYTES * (THREE ? 2 : 1)) * cbs);
-                for (int kb = kb0; kb < kb_end; kb += cbs) {
-                    if (!(ok = mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status))) break;
-                    uint8_t *sa = smem + stage * stage_bytes;
-                    uint8_t *sb = sa + A_STAGE_BYTES * cbs;
+                continue;
+            }
+            int tap = 0, cb = 0, kh = 0, kw = 0;
+            if (kb0) {
+                tap = kb0 / p.c_blocks; cb = kb0 - tap * p.c_blocks;
+                kh = tap / p.ksize_w; kw = tap - kh * p.ksize_w;
+            }
+            const uint32_t tx_bytes = (uint32_t)(((GATHER ? 0 : p.tx_bytes_a) + C::B_STAGE_BYTES * (THREE ? 2 : 1)) * cbs);
+            for (int kb = kb0; kb < kb_end; kb += cbs) {
+                if (!(ok = mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status))) break;
+                uint8_t *sa = smem + stage * stage_bytes;
+                uint8_t *sb = sa + A_STAGE_BYTES * cbs;
+                if (leader) {
                     mbar_expect_tx(&full[stage], tx_bytes);
                     if (cbs == 2) {
                         tma_load_5d(sa, &p.tm_a, &full[stage], 0, w0 + kw, h0 + kh, n0, cb);
                         tma_load_4d(sb, &p.tm_b, &full[stage], 0, n_tile * BLOCK_N, cb, tap);
                     } else {
-                        if (!p.gather) tma_load_4d(sa, &p.tm_a, &full[stage], cb * BLOCK_K, w0 + kw, h0 + kh, n0);
+                        if (!GATHER) tma_load_4d(sa, &p.tm_a, &full[stage], cb * BLOCK_K, w0 + kw, h0 + kh, n0);
                         tma_load_3d(sb, &p.tm_b, &full[stage], cb * BLOCK_K, n_tile * BLOCK_N, tap);
                         if (THREE)
                             tma_load_3d(sb + C::B_STAGE_BYTES + A_STAGE_BYTES, &p.tm_b_lo, &full[stage], cb * BLOCK_K,
                                         n_tile * BLOCK_N, tap);
                     }
-                    if ((cb += cbs) == p.c_blocks) {
-                        cb = 0; tap++;
-                        if (++kw == p.ksize_w) { kw = 0; kh++; }
-                    }
-                    if (++stage == stages) { stage = 0; phase ^= 1; }
                 }
-            }
-            // Tail: the MMA warp's last release of every stage (an mbarrier arrive that the tensor core performs
-            // when those MMAs retire) must have landed in this CTA's shared memory before the CTA may exit.
-            for (int i = 0; i < stages && ok; i++) {
-                ok = mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status);
+                if ((cb += cbs) == p.c_blocks) {
+                    cb = 0; tap++;
+                    if (++kw == p.ksize_w) { kw = 0; kh++; }
+                }
                 if (++stage == stages) { stage = 0; phase ^= 1; }
             }
+        }
+        // Tail: the MMA warp's last release of every stage (an mbarrier arrive that the tensor core performs
+        // when those MMAs retire) must have landed in this CTA's shared memory before the CTA may exit.
+        for (int i = 0; i < stages && ok; i++) {
+            ok = mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status);
+            if (++stage == stages) { stage = 0; phase ^= 1; }
+        }
         }
         __syncwarp();
     } else if (warp == 1) {
         // -------------------------------------------------------- MMA issuer
-        if (elect_one()) {
-            constexpr uint32_t idesc = make_idesc(BLOCK_M, BLOCK_N);
-            int stage = 0;
-            uint32_t phase = 0;
-            int acc = 0;
-            uint32_t acc_phase = 0;
-            bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                if (!(ok = mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag, p.status))) break;
-                tc_fence_after();
-                uint32_t d_tmem = tmem_base + (uint32_t)(acc * acc_cols);
-                int kb_in_part = 0;
-                if (!THREE && p.col3) {
-                    for (int it = 0; it < 3 * p.c_blocks; it++) {
-                        if (!(ok = mbar_wait(&full[stage], phase, abort_flag, p.status))) break;
-                        tc_fence_after();
-                        const uint32_t sa = smem_u32(smem + stage * stage_bytes);
+        // One elected lane.  Its time per MMA is the tensor core's: about 65 cycles for a 128 x 64 x 8 TF32 MMA, 75 for
+        // 128 x 128 x 8 and 138 for 128 x 256 x 8 (the issue blocks while the queue is full), so 64-filter tiles run the
+        // tensor core at about half rate whatever the pipeline around it does.
+        const bool leader = elect_one();
+        if (leader) {
+        constexpr uint32_t idesc = make_idesc(BLOCK_M, BLOCK_N);
+        int stage = 0;
+        uint32_t phase = 0;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            if (!(ok = mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag, p.status))) break;
+            tc_fence_after();
+            uint32_t d_tmem = tmem_base + (uint32_t)(acc * acc_cols);
+            int kb_in_part = 0;
+            if (!THREE && p.col3) {
+                for (int it = 0; it < 3 * p.c_blocks; it++) {
+                    if (!(ok = mbar_wait(&full[stage], phase, abort_flag, p.status))) break;
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem + stage * stage_bytes);
+                    if (leader) {
 #pragma unroll
                         for (int kh3 = 0; kh3 < 3; kh3++) {
                             const uint32_t b_lo = smem_desc_lo(sa + (uint32_t)p.a_box_bytes + kh3 * C::B_STAGE_BYTES);
@@ -278,27 +331,30 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
                             }
                         }
                         umma_commit(&empty[stage]);
-                        if (++stage == stages) { stage = 0; phase ^= 1; }
                     }
-                    if (ok) umma_commit(&acc_full[acc]);
-                    if (++acc == 2) { acc = 0; acc_phase ^= 1; }
-                    continue;
+                    if (++stage == stages) { stage = 0; phase ^= 1; }
                 }
-                const int tile_kb = min(p.kb_per_split, p.num_k_blocks - (tile % p.k_splits) * p.kb_per_split);
-                for (int kb = 0; kb < tile_kb; kb += cbs, kb_in_part += cbs) {
-                    if (kb_in_part == p.kb_per_part) {
-                        // hand this partial sum to the epilogue warps and restart in the other accumulator
-                        umma_commit(&acc_full[acc]);
-                        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
-                        if (!(ok = mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag, p.status))) break;
-                        tc_fence_after();
-                        d_tmem = tmem_base + (uint32_t)(acc * acc_cols);
-                        kb_in_part = 0;
-                    }
-                    uint64_t *ready = (THREE && !p.gather) ? &split[stage] : &full[stage];
-                    if (!(ok = mbar_wait(ready, phase, abort_flag, p.status))) break;
+                if (ok && leader) umma_commit(&acc_full[acc]);
+                if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+                continue;
+            }
+            const int ksplit = p.k_splits > 1 ? tile % p.k_splits : 0;
+            const int tile_kb = min(p.kb_per_split, p.num_k_blocks - ksplit * p.kb_per_split);
+            for (int kb = 0; kb < tile_kb; kb += cbs, kb_in_part += cbs) {
+                if (kb_in_part == p.kb_per_part) {
+                    // hand this partial sum to the epilogue warps and restart in the other accumulator
+                    if (leader) umma_commit(&acc_full[acc]);
+                    if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+                    if (!(ok = mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag, p.status))) break;
                     tc_fence_after();
-                    const uint32_t sa = smem_u32(smem + stage * stage_bytes);
+                    d_tmem = tmem_base + (uint32_t)(acc * acc_cols);
+                    kb_in_part = 0;
+                }
+                uint64_t *ready = (THREE && !GATHER) ? &split[stage] : &full[stage];
+                if (!(ok = mbar_wait(ready, phase, abort_flag, p.status))) break;
+                tc_fence_after();
+                const uint32_t sa = smem_u32(smem + stage * stage_bytes);
+                if (leader) {
                     for (int c = 0; c < cbs; c++) {
                         const uint32_t a_lo = smem_desc_lo(sa + c * A_STAGE_BYTES);
                         const uint32_t b_lo = smem_desc_lo(sa + cbs * A_STAGE_BYTES + c * C::B_STAGE_BYTES);
@@ -317,11 +373,12 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
                         }
                     }
                     umma_commit(&empty[stage]);     // frees the stage once these MMAs have read it
-                    if (++stage == stages) { stage = 0; phase ^= 1; }
                 }
-                if (ok) umma_commit(&acc_full[acc]);
-                if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+                if (++stage == stages) { stage = 0; phase ^= 1; }
             }
+            if (ok && leader) umma_commit(&acc_full[acc]);
+            if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        }
         }
         __syncwarp();
     } else if (warp < 10) {
@@ -342,13 +399,9 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-            const int split = tile % p.k_splits, mn = tile / p.k_splits;
-            const int m_tile = p.m_fastest ? mn % p.m_tiles : mn / p.n_tiles;
-            const int n_tile = p.m_fastest ? mn / p.m_tiles : mn % p.n_tiles;
-            const int tw = m_tile % p.tiles_w;
-            const int th = (m_tile / p.tiles_w) % p.tiles_h;
-            const int tn = m_tile / (p.tiles_w * p.tiles_h);
+        TileIter ti(p, blockIdx.x, gridDim.x);
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ti.next(p)) {
+            const int split = ti.split, n_tile = ti.n_tile, tw = ti.tw, th = ti.th, tn = ti.tn;
             const int ow = tw * p.bw + rw, oh = th * p.bh * halves + rh, n = tn * p.bn + rn;
             const bool row_ok = (rn < p.bn) && ow < p.OW && oh < p.OH && n < p.NB;
             const long row = ((long)n * p.OH + oh) * p.OW + ow;
@@ -376,7 +429,7 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
                         uint32_t v[32];
                         tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * acc_cols + hf * BLOCK_N + chunk * 32), v);
                         tmem_ld_wait();
-                        epilogue_chunk(p.e, &p.tm_y, &p.tm_yp, v, col0, hrow, hbox, slab, bar_id, store_thread, t);
+                        epilogue_chunk<THREE>(p.e, &p.tm_y, &p.tm_yp, v, col0, hrow, hbox, slab, bar_id, store_thread, t);
                     }
                 }
                 tc_fence_before();
@@ -417,12 +470,12 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
                     const int chunk = grp + 2 * ci;
                     const int col0 = n_tile * BLOCK_N + chunk * 32;
                     if (chunk * 32 < BLOCK_N && col0 < p.e.N)
-                        epilogue_chunk(p.e, &p.tm_y, &p.tm_yp, sum[ci], col0, erow, ebox, slab, bar_id, store_thread, t);
+                        epilogue_chunk<THREE>(p.e, &p.tm_y, &p.tm_yp, sum[ci], col0, erow, ebox, slab, bar_id, store_thread, t);
                 }
             }
         }
         if (store_thread) tma_store_wait_all();     // staged tiles must have left shared memory
-    } else if (p.gather) {
+    } else if (GATHER) {
         // ------------------------------------------------- in-kernel patch gather
         // One thread per tile row (output pixel): 32 columns (kh,kw,c) of this K block are read
         // through the cache (neighbouring threads read neighbouring pixels) and written as one
@@ -569,15 +622,19 @@ typedef void (*TcKernel)(const TcParams);
 
 struct Variant { TcKernel kernel; int smem; };
 
-template <int BLOCK_N, bool THREE, bool PROMOTE>
-Variant variant() { return {gemm_tf32_tcgen05_kernel<BLOCK_N, THREE, PROMOTE>, Cfg<BLOCK_N, THREE>::SMEM_BYTES}; }
+template <int BLOCK_N, bool THREE, bool PROMOTE, bool GATHER>
+Variant variant() { return {gemm_tf32_tcgen05_kernel<BLOCK_N, THREE, PROMOTE, GATHER>, Cfg<BLOCK_N, THREE>::SMEM_BYTES}; }
 
-// index: [three][promote][block_n: 0 = 64, 1 = 128, 2 = 256]; absent combinations are null
-const Variant VARIANTS[2][2][3] = {
-    {{variant<64, false, false>(), variant<128, false, false>(), variant<256, false, false>()},
-     {variant<64, false, true>(), variant<128, false, true>(), {nullptr, 0}}},
-    {{{nullptr, 0}, {nullptr, 0}, {nullptr, 0}},
-     {variant<64, true, true>(), variant<128, true, true>(), {nullptr, 0}}},
+// index: [gather][three][promote][block_n: 0 = 64, 1 = 128, 2 = 256]; absent combinations are null
+const Variant VARIANTS[2][2][2][3] = {
+    {{{variant<64, false, false, false>(), variant<128, false, false, false>(), variant<256, false, false, false>()},
+      {variant<64, false, true, false>(), variant<128, false, true, false>(), {nullptr, 0}}},
+     {{{nullptr, 0}, {nullptr, 0}, {nullptr, 0}},
+      {variant<64, true, true, false>(), variant<128, true, true, false>(), {nullptr, 0}}}},
+    {{{variant<64, false, false, true>(), variant<128, false, false, true>(), {nullptr, 0}},
+      {{nullptr, 0}, {nullptr, 0}, {nullptr, 0}}},
+     {{{nullptr, 0}, {nullptr, 0}, {nullptr, 0}},
+      {variant<64, true, true, true>(), variant<128, true, true, true>(), {nullptr, 0}}}},
 };
 
 // One worked-out launch: kernel parameters (tile geometry, tensor maps), kernel variant, grid.
@@ -594,10 +651,11 @@ inline bool aligned16(const void *p) { return ((uintptr_t)p & 15) == 0; }
 }  // namespace
 
 void gemm_tc_prepare_device() {
-    for (auto &t : VARIANTS)
-        for (auto &pr : t)
-            for (auto &v : pr)
-                if (v.kernel) NB_CHECK_CUDA(cudaFuncSetAttribute(v.kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, v.smem));
+    for (auto &g : VARIANTS)
+        for (auto &t : g)
+            for (auto &pr : t)
+                for (auto &v : pr)
+                    if (v.kernel) NB_CHECK_CUDA(cudaFuncSetAttribute(v.kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, v.smem));
 }
 
 void encode_tensor_map(nb_handle_s *h, CUtensorMap *tm, const void *base, int rank, const cuuint64_t *dims,
@@ -848,7 +906,13 @@ std::unique_ptr<TcLaunch> build_launch(nb_handle_s *h, const GemmArgs &a, bool t
         cuuint32_t es[4] = {1, (cuuint32_t)g.stride, (cuuint32_t)g.stride, 1};
         encode(h, &p.tm_a, a.a, 4, dims, strides, bx, es);
     }
-    if (p.cbs == 1) {   // B: dims {Kc, N, taps}
+    if (p.col3) {       // B: dims {Kc, N, kw, kh}; a box is one filter column: kw fixed, kh = 0..2
+        cuuint64_t dims[4] = {(cuuint64_t)kc, (cuuint64_t)a.N, 3, 3};
+        cuuint64_t strides[3] = {(cuuint64_t)a.ldb * 4, (cuuint64_t)a.ldb * 4 * (cuuint64_t)a.N, (cuuint64_t)a.ldb * 12 * (cuuint64_t)a.N};
+        cuuint32_t bx[4] = {(cuuint32_t)BLOCK_K, (cuuint32_t)block_n, 1, 3};
+        cuuint32_t es[4] = {1, 1, 1, 1};
+        encode(h, &p.tm_b, a.b, 4, dims, strides, bx, es);
+    } else if (p.cbs == 1) {   // B: dims {Kc, N, taps}
         cuuint64_t dims[3] = {(cuuint64_t)kc, (cuuint64_t)a.N, (cuuint64_t)taps};
         cuuint64_t strides[2] = {(cuuint64_t)a.ldb * 4, (cuuint64_t)a.ldb * 4 * (cuuint64_t)a.N};
         cuuint32_t bx[3] = {(cuuint32_t)BLOCK_K, (cuuint32_t)block_n, 1};
@@ -875,7 +939,7 @@ std::unique_ptr<TcLaunch> build_launch(nb_handle_s *h, const GemmArgs &a, bool t
         encode(h, &p.tm_yp, a.y_pool, 4, dims, strides, bx, es);
     }
 
-    L->v = VARIANTS[three_pass ? 1 : 0][promote ? 1 : 0][block_n == 256 ? 2 : (block_n == 128 ? 1 : 0)];
+    L->v = VARIANTS[gather ? 1 : 0][three_pass ? 1 : 0][promote ? 1 : 0][block_n == 256 ? 2 : (block_n == 128 ? 1 : 0)];
     if (!L->v.kernel) throw Error(NB_ERR_UNSUPPORTED, "no tensor-core kernel variant for this tile width");
     const int tiles = p.m_tiles * p.n_tiles * p.k_splits;
     L->grid = std::max(1, std::min(tiles, h->sm_count));

@@ -247,6 +247,9 @@ __device__ __forceinline__ void tmem_ld_wait() {
 // scale/shift + bias, optional addend, activation, optional TF32 rounding, then either a swizzled
 // staging slab that leaves by TMA (optionally 2x2/2 max-pooled first) or plain global stores.
 // Called by the 128 threads of one epilogue group; `t` is the thread's index in the group.
+// F64_CELL: the LSTM cell's activations by the reference's double formulas (the 3xTF32 kernels) instead of fp32 ones;
+// a compile-time choice because the double path's registers would otherwise be charged to every epilogue mode.
+template <bool F64_CELL>
 __device__ __forceinline__ void epilogue_chunk(const EpiParams &e, const CUtensorMap *tm_y, const CUtensorMap *tm_yp,
                                                uint32_t (&v)[32], int col0, const EpiRow &rw, const EpiBox &bx,
                                                float4 *slab, int bar_id, bool store_thread, int t) {
@@ -293,7 +296,7 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams &e, const CUtenso
         // the common ones inline, the rest through one out-of-line call per value
         if (e.act == NB_ACT_RELU) {
 #pragma unroll
-            for (int j = 0; j < 32; j++) v[j] = __uint_as_float(v[j]) > 0.0f ? v[j] : 0u;
+            for (int j = 0; j < 32; j++) v[j] = __float_as_uint(fmaxf(__uint_as_float(v[j]), 0.0f));   // NaN and -0 give +0, as x > 0 ? x : 0 does
         } else if (e.act == NB_ACT_LEAKY) {
 #pragma unroll
             for (int j = 0; j < 32; j++) {
@@ -317,42 +320,44 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams &e, const CUtenso
         const int j0 = col0 >> 2;
         if (rw.row_ok && j0 < e.lstm_H) {
             const long idx0 = rw.grow * e.lstm_H + j0;
-            float cp[8], cn[8], hn[8];
-            // all of c_{t-1} first: the eight loads overlap instead of one round trip per unit
-            if (!e.lstm_c_prev) {
+            // four units at a time (the 32 accumulators plus the states of all eight at once cost the other epilogue
+            // modes registers); within a half the loads of c_{t-1} overlap
 #pragma unroll
-                for (int u = 0; u < 8; u++) cp[u] = 0.0f;
-            } else if (e.lstm_vec) {
-                const float4 lo = *reinterpret_cast<const float4 *>(e.lstm_c_prev + idx0);
-                const float4 hi = *reinterpret_cast<const float4 *>(e.lstm_c_prev + idx0 + 4);
-                cp[0] = lo.x; cp[1] = lo.y; cp[2] = lo.z; cp[3] = lo.w; cp[4] = hi.x; cp[5] = hi.y; cp[6] = hi.z; cp[7] = hi.w;
-            } else {
+            for (int q = 0; q < 2; q++) {
+                float cp[4], cn[4], hn[4];
+                const long idx = idx0 + 4 * q;
+                if (!e.lstm_c_prev) {
 #pragma unroll
-                for (int u = 0; u < 8; u++) cp[u] = j0 + u < e.lstm_H ? e.lstm_c_prev[idx0 + u] : 0.0f;
-            }
+                    for (int u = 0; u < 4; u++) cp[u] = 0.0f;
+                } else if (e.lstm_vec) {
+                    const float4 c4 = *reinterpret_cast<const float4 *>(e.lstm_c_prev + idx);
+                    cp[0] = c4.x; cp[1] = c4.y; cp[2] = c4.z; cp[3] = c4.w;
+                } else {
 #pragma unroll
-            for (int u = 0; u < 8; u++) {
-                const float zi = __uint_as_float(v[4 * u]), zf = __uint_as_float(v[4 * u + 1]);
-                const float zg = __uint_as_float(v[4 * u + 2]), zo = __uint_as_float(v[4 * u + 3]);
-                const float2 ch = e.lstm_f32 ? lstm_cell_unit_f32(zi, zf, zg, zo, cp[u]) : lstm_cell_unit(zi, zf, zg, zo, cp[u]);
-                cn[u] = ch.x; hn[u] = ch.y;
-            }
-            if (e.lstm_vec) {
-#pragma unroll
-                for (int q = 0; q < 2; q++) {
-                    *reinterpret_cast<float4 *>(e.lstm_c + idx0 + 4 * q) = make_float4(cn[4 * q], cn[4 * q + 1], cn[4 * q + 2], cn[4 * q + 3]);
-                    *reinterpret_cast<float4 *>(e.lstm_h + idx0 + 4 * q) = make_float4(hn[4 * q], hn[4 * q + 1], hn[4 * q + 2], hn[4 * q + 3]);
-                    if (e.lstm_h_round)
-                        *reinterpret_cast<float4 *>(e.lstm_h_round + idx0 + 4 * q) = make_float4(
-                            round_tf32(hn[4 * q]), round_tf32(hn[4 * q + 1]), round_tf32(hn[4 * q + 2]), round_tf32(hn[4 * q + 3]));
+                    for (int u = 0; u < 4; u++) cp[u] = j0 + 4 * q + u < e.lstm_H ? e.lstm_c_prev[idx + u] : 0.0f;
                 }
-            } else {
 #pragma unroll
-                for (int u = 0; u < 8; u++) {
-                    if (j0 + u < e.lstm_H) {
-                        e.lstm_c[idx0 + u] = cn[u];
-                        e.lstm_h[idx0 + u] = hn[u];
-                        if (e.lstm_h_round) e.lstm_h_round[idx0 + u] = round_tf32(hn[u]);
+                for (int u = 0; u < 4; u++) {
+                    const int c = 4 * (4 * q + u);
+                    const float zi = __uint_as_float(v[c]), zf = __uint_as_float(v[c + 1]);
+                    const float zg = __uint_as_float(v[c + 2]), zo = __uint_as_float(v[c + 3]);
+                    const float2 ch = F64_CELL ? lstm_cell_unit(zi, zf, zg, zo, cp[u]) : lstm_cell_unit_f32(zi, zf, zg, zo, cp[u]);
+                    cn[u] = ch.x; hn[u] = ch.y;
+                }
+                if (e.lstm_vec) {
+                    *reinterpret_cast<float4 *>(e.lstm_c + idx) = make_float4(cn[0], cn[1], cn[2], cn[3]);
+                    *reinterpret_cast<float4 *>(e.lstm_h + idx) = make_float4(hn[0], hn[1], hn[2], hn[3]);
+                    if (e.lstm_h_round)
+                        *reinterpret_cast<float4 *>(e.lstm_h_round + idx) =
+                            make_float4(round_tf32(hn[0]), round_tf32(hn[1]), round_tf32(hn[2]), round_tf32(hn[3]));
+                } else {
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        if (j0 + 4 * q + u < e.lstm_H) {
+                            e.lstm_c[idx + u] = cn[u];
+                            e.lstm_h[idx + u] = hn[u];
+                            if (e.lstm_h_round) e.lstm_h_round[idx + u] = round_tf32(hn[u]);
+                        }
                     }
                 }
             }
