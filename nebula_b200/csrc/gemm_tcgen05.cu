@@ -662,7 +662,7 @@ void encode_tensor_map(nb_handle_s *h, CUtensorMap *tm, const void *base, int ra
                        const cuuint64_t *strides_bytes, const cuuint32_t *box, const cuuint32_t *elem_strides) {
     CUresult r = h->encode_tiled(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, const_cast<void *>(base), dims,
                                  strides_bytes, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) throw Error(NB_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
 }
