@@ -793,11 +793,22 @@ std::unique_ptr<TcLaunch> build_launch(nb_handle_s *h, const GemmArgs &a, bool t
     int block_n = 256;
     if (three_pass || gather || promote) block_n = 128;
     if (a.block_n_hint) block_n = std::min(block_n, a.block_n_hint);
-    while (block_n > 64 && !a.block_n_hint) {
-        const long tiles = (long)p.m_tiles * S * ((a.N + block_n - 1) / block_n);
-        if (a.N > block_n / 2 && tiles >= h->sm_count) break;
-        if (a.N > block_n / 2 && (long)p.m_tiles * ((a.N + block_n / 2 - 1) / (block_n / 2)) > 2L * h->sm_count) break;
-        block_n /= 2;
+    if (!a.block_n_hint) {
+        // Cost of a K block of a 128 x bn tile: its MMAs (128 / 64 / 48 cycles per K = 8 step at bn = 256 / 128 / 64) or
+        // the operand bytes it needs at the ~71 B/cycle/SM that L2 delivers to 148 SMs loading at once, whichever is
+        // larger; times the number of waves of tiles.  Wider tiles move fewer bytes per FLOP, so a single wave of
+        // 256-wide tiles on two thirds of the SMs beats two waves of 128-wide ones (conv5_x at 32 images per GPU).
+        const int widest = block_n;
+        long best_cost = 0;
+        for (int bn = widest; bn >= 64; bn /= 2) {
+            if (bn > 64 && a.N <= bn / 2) continue;         // more than half of the tile would be padding
+            const long tiles = (long)p.m_tiles * S * ((a.N + bn - 1) / bn);
+            const long waves = (tiles + h->sm_count - 1) / h->sm_count;
+            const long mma = bn == 256 ? 512 : (bn == 128 ? 256 : 192);
+            const long supply = (long)(BLOCK_M + bn) * BLOCK_K * 4 / 71;
+            const long cost = waves * std::max(mma, supply);
+            if (best_cost == 0 || cost < best_cost) { best_cost = cost; block_n = bn; }
+        }
     }
     p.n_tiles = (a.N + block_n - 1) / block_n;
     p.m_fastest = (!a.a_is_conv && !gather && (size_t)a.N * a.Kc * 4 > ((size_t)48 << 20)) ? 1 : 0;
