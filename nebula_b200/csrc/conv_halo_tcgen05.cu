@@ -221,7 +221,7 @@ __global__ void __launch_bounds__(320, 1) conv3x3_halo_tcgen05_kernel(const __gr
                 uint32_t v[32];
                 tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * acc_cols + hf * BLOCK_N + chunk * 32), v);
                 tmem_ld_wait();
-                epilogue_chunk<false>(p.e, &p.tm_y, &p.tm_yp, v, col0, rw, bx, slab, bar_id, store_thread, t);
+                epilogue_chunk<false>(p.e, &p.tm_y, &p.tm_yp, v, col0, rw, bx, slab, bar_id, store_thread, t, 0, [] {});
             }
             tc_fence_before();
             mbar_arrive(&acc_empty[acc]);

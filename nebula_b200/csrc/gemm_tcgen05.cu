@@ -86,6 +86,10 @@ struct TcParams {
     // (bh * halves + 2 image rows, the second half 8 image rows further down) and the same three weight tiles, which
     // halves the weight traffic per pixel; each half has its own accumulator columns.
     int halves;
+    // Byte offset (from the ring's start) of a second staging buffer per epilogue group, or 0.  A bulk store takes over
+    // a thousand cycles to read its 16 KB out of shared memory; where the ring leaves room, a group alternates between
+    // two buffers and lets one store read while the next slab is staged.
+    int slab2_offset;
     EpiParams e;                // fused epilogue
     // gather mode: warps 6-9 build the A tile in shared memory from a strided activation tensor
     // (channel counts TMA cannot address, e.g. the 3-channel input layer); rows are output pixels
@@ -244,7 +248,7 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
                 // (tm_b is 4-D here, {C, N, kw, kh}: a box of one kw and all three kh)
                 const uint32_t tx3 = (uint32_t)(p.a_box_bytes + 3 * C::B_STAGE_BYTES);
                 for (int cb3 = 0; cb3 < p.c_blocks && ok; cb3++) {       // kw fastest, then the channel slice
-                    for (int kw3 = 0; kw3 < 3; kw3++) {
+                    for (int kw3 = 0; kw3 < p.ksize_w; kw3++) {
                         if (!(ok = mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status))) break;
                         uint8_t *sa = smem + stage * stage_bytes;
                         if (leader) {
@@ -314,7 +318,7 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
             uint32_t d_tmem = tmem_base + (uint32_t)(acc * acc_cols);
             int kb_in_part = 0;
             if (!THREE && p.col3) {
-                for (int it = 0; it < 3 * p.c_blocks; it++) {
+                for (int it = 0; it < p.ksize_w * p.c_blocks; it++) {
                     if (!(ok = mbar_wait(&full[stage], phase, abort_flag, p.status))) break;
                     tc_fence_after();
                     const uint32_t sa = smem_u32(smem + stage * stage_bytes);
@@ -395,7 +399,10 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
         const int rw = r % p.bw, rh = (r / p.bw) % p.bh, rn = r / (p.bw * p.bh);
         const bool store_thread = t == 0;
         constexpr int CH = BLOCK_N >= 64 ? BLOCK_N / 64 : 1;    // 32-column slabs per group
-        float4 *slab = reinterpret_cast<float4 *>(out_stage + grp * C::OUT_STAGE_BYTES);
+        float4 *slab0 = reinterpret_cast<float4 *>(out_stage + grp * C::OUT_STAGE_BYTES);
+        float4 *slab1 = p.slab2_offset ? reinterpret_cast<float4 *>(smem + p.slab2_offset + grp * C::OUT_STAGE_BYTES) : slab0;
+        const int stores_in_flight = p.slab2_offset ? 1 : 0;
+        float4 *slab = slab0;
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
@@ -410,6 +417,8 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
             if (!PROMOTE || p.parts == 1) {
                 if (!(ok = epilogue_all(mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status), bar_id))) break;
                 tc_fence_after();
+                uint32_t v[32];
+                bool loaded = false;            // v holds a tcgen05.ld issued while the previous slab was being stored
 #pragma unroll 1
                 for (int hf = 0; hf < halves; hf++) {
                     // the second half of a two-box tile: the same raster p.bh image rows further down
@@ -426,10 +435,18 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
                     for (int chunk = grp; chunk < BLOCK_N / 32; chunk += 2) {
                         const int col0 = n_tile * BLOCK_N + chunk * 32;
                         if (col0 >= p.e.N) break;         // uniform across the group
-                        uint32_t v[32];
-                        tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * acc_cols + hf * BLOCK_N + chunk * 32), v);
+                        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * acc_cols + hf * BLOCK_N + chunk * 32);
+                        if (!loaded) tmem_ld_32x32(taddr, v);
                         tmem_ld_wait();
-                        epilogue_chunk<THREE>(p.e, &p.tm_y, &p.tm_yp, v, col0, hrow, hbox, slab, bar_id, store_thread, t);
+                        loaded = false;
+                        // this group's next slab of the tile: the next pair of columns, else the first of the other half
+                        uint32_t next = 0;
+                        if (PROMOTE) {}         // (those variants have no registers to spare for it)
+                        else if (chunk + 2 < BLOCK_N / 32 && col0 + 64 < p.e.N) next = taddr + 64;
+                        else if (hf + 1 < halves) next = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * acc_cols + (hf + 1) * BLOCK_N + grp * 32);
+                        epilogue_chunk<THREE>(p.e, &p.tm_y, &p.tm_yp, v, col0, hrow, hbox, slab, bar_id, store_thread, t, stores_in_flight,
+                                              [&] { if (next) { tmem_ld_32x32(next, v); loaded = true; } });
+                        slab = slab == slab0 ? slab1 : slab0;
                     }
                 }
                 tc_fence_before();
@@ -470,7 +487,7 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
                     const int chunk = grp + 2 * ci;
                     const int col0 = n_tile * BLOCK_N + chunk * 32;
                     if (chunk * 32 < BLOCK_N && col0 < p.e.N)
-                        epilogue_chunk<THREE>(p.e, &p.tm_y, &p.tm_yp, sum[ci], col0, erow, ebox, slab, bar_id, store_thread, t);
+                        epilogue_chunk<THREE>(p.e, &p.tm_y, &p.tm_yp, sum[ci], col0, erow, ebox, slab0, bar_id, store_thread, t, 0, [] {});
                 }
             }
         }
@@ -734,8 +751,11 @@ std::unique_ptr<TcLaunch> build_launch(nb_handle_s *h, const GemmArgs &a, bool t
     Box box = choose_box(g.OW, g.OH, g.batch, g.stride, pool, S > 1, (double)g.sn * 4.0);
     // filter-column stages: 3x3 / stride 1, at most 128 input channels and filters (the layers that are bound by
     // re-loading activations from L2), a fixed 16 x 8 pixel box; not worth it when the box wastes much of the plane
-    const bool col3 = a.a_is_conv && !gather && !three_pass && S == 1 && g.ksize == 3 && ksize_w == 3 && g.stride == 1 &&
-                      g.pad <= 1 && (g.pad_w < 0 || g.pad_w == g.pad) && kc <= 128 && a.N <= 128 && g.OW >= 16 && g.OH >= 8 &&
+    // (the row-window layout of a layer with <= 4 input channels has the filter columns folded into its "channels":
+    // three filter rows, one column, no padding in w)
+    const bool col3 = a.a_is_conv && !gather && !three_pass && S == 1 && g.ksize == 3 && g.stride == 1 && g.pad <= 1 &&
+                      ((ksize_w == 3 && (g.pad_w < 0 || g.pad_w == g.pad)) || (ksize_w == 1 && g.pad_w == 0)) &&
+                      kc <= 128 && a.N <= 128 && g.OW >= 16 && g.OH >= 8 &&
                       ((double)g.OW / ((g.OW + 15) / 16 * 16)) * ((double)g.OH / ((g.OH + 7) / 8 * 8)) >= 0.8;
     if (col3) box = Box{16, 8, 1};
     // two boxes per tile when the plane is tall enough for 16-row tiles not to waste much of it
@@ -832,6 +852,12 @@ std::unique_ptr<TcLaunch> build_launch(nb_handle_s *h, const GemmArgs &a, bool t
         p.a_box_bytes = BLOCK_K * 4 * box.bw * (box.bh * halves + 2);
         p.stage_bytes = p.col3 ? p.a_box_bytes + 3 * b_stage : stage1 * p.cbs;
         p.stages = std::min(8, ring / p.stage_bytes);
+        // a second staging buffer per epilogue group in what the ring leaves unused; a one-column filter (row windows:
+        // one stage per tile, bound by its epilogue) gives up its third stage for it
+        if (p.col3 && ksize_w == 1 && p.stages > 2) p.stages = 2;
+        const int ring_cap = std::min(8, (196 * 1024) / stage1) * stage1;
+        const int used = p.stages * p.stage_bytes;
+        p.slab2_offset = (!three_pass && !promote && !gather && ring_cap - used >= 2 * BLOCK_M * 32 * 4) ? used : 0;
     }
     p.gather = gather ? 1 : 0;
     if (gather) {
@@ -918,8 +944,9 @@ std::unique_ptr<TcLaunch> build_launch(nb_handle_s *h, const GemmArgs &a, bool t
         encode(h, &p.tm_a, a.a, 4, dims, strides, bx, es);
     }
     if (p.col3) {       // B: dims {Kc, N, kw, kh}; a box is one filter column: kw fixed, kh = 0..2
-        cuuint64_t dims[4] = {(cuuint64_t)kc, (cuuint64_t)a.N, 3, 3};
-        cuuint64_t strides[3] = {(cuuint64_t)a.ldb * 4, (cuuint64_t)a.ldb * 4 * (cuuint64_t)a.N, (cuuint64_t)a.ldb * 12 * (cuuint64_t)a.N};
+        cuuint64_t dims[4] = {(cuuint64_t)kc, (cuuint64_t)a.N, (cuuint64_t)ksize_w, 3};
+        cuuint64_t strides[3] = {(cuuint64_t)a.ldb * 4, (cuuint64_t)a.ldb * 4 * (cuuint64_t)a.N,
+                                 (cuuint64_t)a.ldb * 4 * (cuuint64_t)a.N * (cuuint64_t)ksize_w};
         cuuint32_t bx[4] = {(cuuint32_t)BLOCK_K, (cuuint32_t)block_n, 1, 3};
         cuuint32_t es[4] = {1, 1, 1, 1};
         encode(h, &p.tm_b, a.b, 4, dims, strides, bx, es);

@@ -249,10 +249,16 @@ __device__ __forceinline__ void tmem_ld_wait() {
 // Called by the 128 threads of one epilogue group; `t` is the thread's index in the group.
 // F64_CELL: the LSTM cell's activations by the reference's double formulas (the 3xTF32 kernels) instead of fp32 ones;
 // a compile-time choice because the double path's registers would otherwise be charged to every epilogue mode.
-template <bool F64_CELL>
+// `stores_in_flight`: bulk stores of this group that may still be reading their staging buffer when this slab's
+// buffer is written (1 when the group alternates between two buffers, else 0).  `staged()` is called once the
+// accumulators have left the registers (staged in shared memory): the caller starts the next `tcgen05.ld` there, so
+// that its latency passes behind the fence, the barrier and the store; it is not called in the modes that keep
+// the values in registers to the end (plain stores, the LSTM cell).
+template <bool F64_CELL, class Staged>
 __device__ __forceinline__ void epilogue_chunk(const EpiParams &e, const CUtensorMap *tm_y, const CUtensorMap *tm_yp,
                                                uint32_t (&v)[32], int col0, const EpiRow &rw, const EpiBox &bx,
-                                               float4 *slab, int bar_id, bool store_thread, int t) {
+                                               float4 *slab, int bar_id, bool store_thread, int t, int stores_in_flight,
+                                               Staged &&staged) {
     const bool full_cols = col0 + 32 <= e.N;
     // affine part: folded batch-norm scale/shift + bias (vectors padded to a multiple of 32)
     if (e.scale) {
@@ -366,12 +372,17 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams &e, const CUtenso
     }
     if (!e.addend_post) activate();
     if (e.round_out) {
+        // (cvt.rna.tf32.f32 runs at 32 per cycle per SM; (bits + 0x1000) & 0xFFFFE000 gives the same bits for every
+        // input that is not a NaN, but sending half of the values through the integer pipe instead measured no faster)
 #pragma unroll
         for (int j = 0; j < 32; j++) v[j] = __float_as_uint(round_tf32(__uint_as_float(v[j])));
     }
     if (e.pool || e.tma_store) {
         // the group's previous store must have finished reading the staging buffer
-        if (store_thread) tma_store_wait_read<0>();
+        if (store_thread) {
+            if (stores_in_flight) tma_store_wait_read<1>();
+            else tma_store_wait_read<0>();
+        }
         epilogue_bar_sync(bar_id);
         if (rw.srow >= 0) {
 #pragma unroll
@@ -379,6 +390,7 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams &e, const CUtenso
             slab[rw.srow * 8 + (j ^ (rw.srow & 7))] = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
                                                      __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
         }
+        staged();
         if (!e.pool) {
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             epilogue_bar_sync(bar_id);
