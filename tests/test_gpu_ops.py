@@ -34,9 +34,14 @@ CONV_CASES = [
     (2, 32, 31, 31, 16, 11, 4, 0, False, "relu"),       # 11x11 stride 4
     (5, 128, 7, 7, 256, 3, 1, 1, False, "relu"),        # several images per pixel box
     (1, 32, 40, 36, 300, 3, 1, 0, False, "tanh"),       # no padding, F tail over 256
-    (2, 64, 28, 42, 64, 3, 1, 1, False, "relu"),        # 3x3 halo kernel: two 128-row halves, exact tiles in W
-    (1, 128, 33, 56, 160, 3, 1, 1, True, "leaky"),      # halo kernel: C=128, ragged tiles in H, filter tail
-    (3, 32, 16, 28, 40, 3, 1, 0, False, "linear"),      # halo kernel without padding
+    (2, 64, 28, 42, 64, 3, 1, 1, False, "relu"),        # filter-column stages, ragged 16 x 8 boxes in both directions
+    (1, 128, 33, 56, 160, 3, 1, 1, True, "leaky"),      # C=128, ragged tiles in H, filter tail
+    (3, 32, 16, 28, 40, 3, 1, 0, False, "linear"),      # filter-column stages without padding
+    (2, 64, 32, 48, 128, 3, 1, 1, True, "relu"),        # filter-column stages, two boxes per tile
+    (2, 3, 24, 32, 24, 3, 1, 1, False, "relu"),         # row windows as one filter column per tile (one box)
+    (2, 3, 32, 64, 64, 3, 1, 1, False, "relu"),         # row windows, two boxes per tile, two staging buffers per group
+    (1, 4, 36, 48, 64, 3, 1, 1, True, "leaky"),         # four input channels, ragged in H
+    (1, 3, 34, 34, 16, 3, 1, 0, False, "linear"),       # row windows without padding
 ]
 
 
