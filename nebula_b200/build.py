@@ -17,7 +17,7 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIBDIR = PKG / "lib"
 LIB = LIBDIR / "libnebula_b200.so"
-SOURCES = ["api.cu", "network.cu", "plans.cu", "elementwise.cu", "gemm_simt.cu", "gemm_tcgen05.cu", "conv_halo_tcgen05.cu", "static_scratch.cu", "arena.cu"]
+SOURCES = ["api.cu", "network.cu", "plans.cu", "elementwise.cu", "gemm_simt.cu", "gemm_tcgen05.cu", "conv_halo_tcgen05.cu", "static_scratch.cu", "arena.cu", "lstm_persistent.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-Xptxas", "-v"]
 

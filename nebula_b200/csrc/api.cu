@@ -74,6 +74,11 @@ int nb_create(int device_id, nb_handle_t *handle) {
                                                 std::to_string(prop.major) + std::to_string(prop.minor));
         NB_CHECK_CUDA(cudaMalloc((void **)&h->d_status, sizeof(int)));
         NB_CHECK_CUDA(cudaMemset(h->d_status, 0, sizeof(int)));
+        NB_CHECK_CUDA(cudaMalloc((void **)&h->d_grid_sync, sizeof(unsigned int)));
+        NB_CHECK_CUDA(cudaMemset(h->d_grid_sync, 0, sizeof(unsigned int)));
+        int coop = 0;
+        NB_CHECK_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, device_id));
+        h->cooperative_launch = coop != 0;
         void *fn = nullptr;
         cudaDriverEntryPointQueryResult qres;
         NB_CHECK_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
@@ -101,12 +106,14 @@ int nb_create(int device_id, nb_handle_t *handle) {
             }
         }
         gemm_tc_prepare_device();
+        lstm_persistent_prepare_device();
         conv_halo_prepare_device();
         elementwise_prepare_device();
     });
     if (rc != NB_OK) {
         g_create_error = h->last_error;
         if (h->d_status) cudaFree(h->d_status);
+        if (h->d_grid_sync) cudaFree(h->d_grid_sync);
         delete h;
         return rc;
     }
@@ -119,6 +126,7 @@ int nb_destroy(nb_handle_t h) {
     cudaSetDevice(h->device);
     cudaStreamSynchronize(h->stream);
     if (h->d_status) cudaFree(h->d_status);
+    if (h->d_grid_sync) cudaFree(h->d_grid_sync);
     for (auto e : h->event_pool) cudaEventDestroy(e);
     for (auto &t : h->timed) { cudaEventDestroy(t.start); cudaEventDestroy(t.stop); }
     delete h;

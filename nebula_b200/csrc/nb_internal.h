@@ -62,6 +62,8 @@ struct nb_handle_s {
     int cc_major = 0;
     std::string last_error;
     int *d_status = nullptr;            // device status word (nb::DEV_*)
+    unsigned int *d_grid_sync = nullptr; // arrival counter of the persistent LSTM kernel's grid barrier
+    bool cooperative_launch = false;    // the device co-schedules the CTAs of a cooperative launch
     nb_encode_tiled_fn encode_tiled = nullptr;
     nb_get_address_range_fn get_address_range = nullptr;   // cuMemGetAddressRange: the allocation a pointer lies in
     unsigned long long launches = 0;
@@ -320,6 +322,10 @@ std::string gemm_args_key(const GemmArgs &a, char tag, int extra);
 
 // Per-device set-up of the tensor-core kernels (shared-memory limits; also loads their code), once per handle.
 void gemm_tc_prepare_device();
+void lstm_persistent_prepare_device();
+bool lstm_persistent_supported(const nb_handle_s *h, int T, int B, int H);
+void lstm_persistent(nb_handle_s *h, const float *w_hi, const float *pre, float *cell, float *out, float *hr, int T, int B,
+                     int H, int t_first);
 void conv_halo_prepare_device();
 void elementwise_prepare_device();
 

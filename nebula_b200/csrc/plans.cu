@@ -551,6 +551,17 @@ void LstmPlan::forward(const float *x, float *out, float *cell, bool x_rounded, 
     // 2. the recurrence: z_t = pre_t + act(h_{t-1} * W^T + bW), then the cell update.  With linear gate layers
     //    step 0 has nothing to multiply (h_{-1} = 0 and bW is already in pre); otherwise act(bW) is not zero and
     //    step 0 runs the recurrent layer on a zero state like every other step.
+    // With linear gate layers on the TF32 tensor-core path, steps 1 .. T-1 run as one cooperative kernel that keeps
+    // the recurrent weights in shared memory (lstm_persistent.cu); step 0 is the cell update alone.
+    const char *lp_env = std::getenv("NEBULA_B200_LSTM_PERSISTENT");
+    bool persistent = tc_w && !three && linear && hr && (H % 8) == 0 && lstm_persistent_supported(h, T, B, H) &&
+                      !(lp_env && *lp_env == '0');
+    if (persistent) {
+        launch_lstm_cell(h, pre.p, nullptr, cell, out, hr, B, H);
+        ww.ensure_split(h);
+        lstm_persistent(h, ww.hi.p, pre.p, cell, out, hr, T, B, H, 1);
+        return;
+    }
     for (int t = 0; t < T; t++) {
         const float *zt = pre.p + (size_t)t * B * 4 * H;
         float *ct = cell + (size_t)t * B * H, *ht = out + (size_t)t * B * H, *hrt = hr ? hr + (size_t)t * B * H : nullptr;

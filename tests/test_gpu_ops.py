@@ -267,6 +267,35 @@ def test_lstm(handle, mode, case):
     assert_close(out.cpu().numpy(), ref, mode, f"lstm {case}")
 
 
+@pytest.mark.parametrize("case", [(6, 16, 64, 64, False), (9, 64, 96, 256, True), (5, 128, 64, 1024, False)],
+                         ids=lambda c: "x".join(map(str, c)))
+def test_lstm_one_kernel_recurrence_is_bit_identical(handle, case, monkeypatch):
+    """TF32 mode runs steps 1..T-1 as one cooperative kernel (weights resident in shared memory, a grid barrier per
+    step); NEBULA_B200_LSTM_PERSISTENT=0 selects the launch-per-step path.  Same K order, same cell arithmetic:
+    hidden and cell states must agree bit for bit."""
+    import torch
+    from nebula_b200 import api
+    from nebula_b200.workloads import NetBuilder
+    T, B, inp, H, bn = case
+    b = NetBuilder("l", B, input_size=inp, time_steps=T, bias_init="bias_n01")
+    b.lstm(H, bn=bn, bound=0.3)
+    wl = b.build("normal")
+    w = wl.make_weights(31)
+    x = _t(wl.make_input(32))
+    handle.set_math("tf32")
+    plan = api.Lstm(handle, T, B, inp, H, bn, "linear")
+    plan.set_weights(w)
+    monkeypatch.setenv("NEBULA_B200_LSTM_PERSISTENT", "0")
+    out0, cell0 = plan.forward(x, want_cell=True)
+    out0, cell0 = out0.clone(), cell0.clone()
+    monkeypatch.delenv("NEBULA_B200_LSTM_PERSISTENT")
+    out1, cell1 = plan.forward(x, want_cell=True)
+    handle.synchronize()
+    plan.close()
+    assert torch.isfinite(out1).all()
+    assert torch.equal(out0, out1) and torch.equal(cell0, cell1)
+
+
 def test_error_reporting(handle):
     """Bad arguments come back as status codes with a message, never as exits."""
     from nebula_b200 import api
