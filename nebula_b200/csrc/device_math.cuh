@@ -70,6 +70,15 @@ static __device__ __noinline__ float2 lstm_cell_unit(float zi, float zf, float z
 // The same update with the gate activations evaluated in fp32 (expf/tanhf, a few ulp from the double formulas):
 // used by the TF32 GEMM epilogue, where the pre-activations already carry ~1e-3 of operand rounding and the few
 // epilogue threads of a small-batch step cannot hide double-precision latency.
+__device__ __forceinline__ float2 lstm_cell_unit_f32_inline(float zi, float zf, float zg, float zo, float c_prev) {
+    const float ig = 1.0f / (1.0f + expf(-zi));
+    const float fg = 1.0f / (1.0f + expf(-zf));
+    const float gg = tanhf(zg);
+    const float og = 1.0f / (1.0f + expf(-zo));
+    const float c = __fadd_rn(__fmul_rn(c_prev, fg), __fmul_rn(ig, gg));
+    return make_float2(c, __fmul_rn(tanhf(c), og));
+}
+// (out of line for the GEMM epilogue, which has no registers to spare; the same operations in the same order)
 static __device__ __noinline__ float2 lstm_cell_unit_f32(float zi, float zf, float zg, float zo, float c_prev) {
     const float ig = 1.0f / (1.0f + expf(-zi));
     const float fg = 1.0f / (1.0f + expf(-zf));

@@ -26,13 +26,15 @@ using namespace tc;
 namespace {
 
 constexpr int LP_N = 32;                    // gate columns per CTA
-constexpr int LP_STAGES = 4;                // ring of A (h) K blocks, 128 rows x 128 bytes each
+constexpr int LP_STAGES = 4;                // most ring stages (barrier slots)
 constexpr int LP_THREADS = 192;             // warps 0-3: epilogue and grid barrier; warp 4: MMA issue; warp 5: TMA
 constexpr int LP_W_TILE = LP_N * 128;       // one K block of the weight slice: 32 rows x 128 bytes
 
 struct LstmPParams {
     CUtensorMap tm_w;           // recurrent weights [4H rows][H], box {32, 32}
-    CUtensorMap tm_h;           // rounded hidden states [T*B rows][H], box {32, B}
+    CUtensorMap tm_h;           // rounded hidden states as {32, T*B rows, H/32}, box {32, B, cbs}
+    int cbs;                    // K blocks per ring stage and TMA request (2 when B % 8 == 0 and H % 64 == 0)
+    int stages, stage_bytes;    // ring geometry: a stage holds cbs slices of B rows and the 128-row window of the last
     const float *pre;           // [T][B][4H] input-side pre-activations (biases included), columns [unit][i,f,g,o]
     const float *hr;            // [T][B][H] rounded hidden states: step t reads [t-1], writes [t]
     float *hr_w;                // the same tensor, for writing
@@ -58,7 +60,8 @@ __global__ void __launch_bounds__(LP_THREADS, 1) lstm_persistent_kernel(const __
     const int KB = p.H / BLOCK_K;                           // K blocks per step
     uint8_t *w_smem = smem;                                  // [KB][32 rows][128 B], swizzled by TMA
     uint8_t *a_ring = smem + (size_t)KB * LP_W_TILE;         // [LP_STAGES][128 rows][128 B]
-    uint64_t *bars = (uint64_t *)(a_ring + LP_STAGES * A_STAGE_BYTES);
+    const int stages = p.stages, stage_bytes = p.stage_bytes, cbs = p.cbs;
+    uint64_t *bars = (uint64_t *)(a_ring + stages * stage_bytes);
     uint64_t *full = bars;                  // loaders -> MMA   [LP_STAGES]
     uint64_t *empty = bars + LP_STAGES;     // MMA -> loaders   [LP_STAGES]
     uint64_t *w_full = bars + 2 * LP_STAGES;
@@ -85,7 +88,7 @@ __global__ void __launch_bounds__(LP_THREADS, 1) lstm_persistent_kernel(const __
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     // rows of the A tiles that no batch row fills: the MMA reads all 128, give them a defined value once
-    for (int i = threadIdx.x; i < LP_STAGES * A_STAGE_BYTES / 16; i += blockDim.x)
+    for (int i = threadIdx.x; i < stages * stage_bytes / 16; i += blockDim.x)
         reinterpret_cast<float4 *>(a_ring)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     tc_fence_before();
@@ -106,23 +109,25 @@ __global__ void __launch_bounds__(LP_THREADS, 1) lstm_persistent_kernel(const __
             int stage = 0;
             uint32_t phase = 0;
             for (int t = p.t_first; t < p.T && ok; t++) {
-                for (int kb = 0; kb < KB; kb++) {
+                for (int kb = 0; kb < KB; kb += cbs) {
                     if (!(ok = mbar_wait(&full[stage], phase, abort_flag, p.status))) break;
                     tc_fence_after();
-                    const uint32_t a_lo = smem_desc_lo(smem_u32(a_ring + stage * A_STAGE_BYTES));
-                    const uint32_t b_lo = smem_desc_lo(smem_u32(w_smem + kb * LP_W_TILE));
+                    for (int c = 0; c < cbs; c++) {
+                        const uint32_t a_lo = smem_desc_lo(smem_u32(a_ring + stage * stage_bytes + c * p.B * 128));
+                        const uint32_t b_lo = smem_desc_lo(smem_u32(w_smem + (kb + c) * LP_W_TILE));
 #pragma unroll
-                    for (int k = 0; k < BLOCK_K / UMMA_K; k++)
-                        umma_tf32(tmem_base, smem_desc(a_lo + 2 * k), smem_desc(b_lo + 2 * k), idesc, (kb | k) != 0);
+                        for (int k = 0; k < BLOCK_K / UMMA_K; k++)
+                            umma_tf32(tmem_base, smem_desc(a_lo + 2 * k), smem_desc(b_lo + 2 * k), idesc, (kb | c | k) != 0);
+                    }
                     umma_commit(&empty[stage]);
-                    if (++stage == LP_STAGES) { stage = 0; phase ^= 1; }
+                    if (++stage == stages) { stage = 0; phase ^= 1; }
                 }
                 if (ok) umma_commit(acc_full);
             }
             // the last releases of the ring must have landed before the CTA may exit
-            for (int i = 0; i < LP_STAGES && ok; i++) {
+            for (int i = 0; i < stages && ok; i++) {
                 ok = mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status);
-                if (++stage == LP_STAGES) { stage = 0; phase ^= 1; }
+                if (++stage == stages) { stage = 0; phase ^= 1; }
             }
         }
         __syncwarp();
@@ -131,7 +136,7 @@ __global__ void __launch_bounds__(LP_THREADS, 1) lstm_persistent_kernel(const __
         if (elect_one()) {
             int stage = 0;
             uint32_t phase = 0, go_phase = 0;
-            const uint32_t tx = (uint32_t)(p.B * BLOCK_K * 4);
+            const uint32_t tx = (uint32_t)(p.B * BLOCK_K * 4 * cbs);
             for (int t = p.t_first; t < p.T && ok; t++) {
                 if (t > p.t_first) {
                     // the other CTAs' stores of h_{t-1} (generic proxy) are ordered before the acquire that opened the
@@ -140,11 +145,11 @@ __global__ void __launch_bounds__(LP_THREADS, 1) lstm_persistent_kernel(const __
                     go_phase ^= 1;
                     asm volatile("fence.proxy.async;" ::: "memory");
                 }
-                for (int kb = 0; kb < KB; kb++) {
+                for (int kb = 0; kb < KB; kb += cbs) {
                     if (!(ok = mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status))) break;
                     mbar_expect_tx(&full[stage], tx);
-                    tma_load_2d(a_ring + stage * A_STAGE_BYTES, &p.tm_h, &full[stage], kb * BLOCK_K, (t - 1) * p.B);
-                    if (++stage == LP_STAGES) { stage = 0; phase ^= 1; }
+                    tma_load_3d(a_ring + stage * stage_bytes, &p.tm_h, &full[stage], 0, (t - 1) * p.B, kb);
+                    if (++stage == stages) { stage = 0; phase ^= 1; }
                 }
             }
         }
@@ -166,6 +171,14 @@ __global__ void __launch_bounds__(LP_THREADS, 1) lstm_persistent_kernel(const __
         for (int t = p.t_first; t < p.T && ok; t++) {
             // gates of this CTA's 8 units for row `tid`; threads only leave the loop together, at the votes, so that
             // none is left alone at a barrier
+            // the input-side pre-activations of this step come from DRAM: fetched while the MMAs run
+            const size_t row = (size_t)t * p.B + tid;
+            float4 z4[8];
+            if (row_ok) {
+                const float4 *zin = reinterpret_cast<const float4 *>(p.pre + row * 4 * p.H + n0);
+#pragma unroll
+                for (int u = 0; u < 8; u++) z4[u] = __ldg(zin + u);
+            }
             ok = epilogue_all(mbar_wait(acc_full, acc_phase, abort_flag, p.status), 1);
             if (!ok) break;
             acc_phase ^= 1;
@@ -175,15 +188,12 @@ __global__ void __launch_bounds__(LP_THREADS, 1) lstm_persistent_kernel(const __
             tmem_ld_wait();
             tc_fence_before();
             if (row_ok) {
-                const size_t row = (size_t)t * p.B + tid;
-                const float *zin = p.pre + row * 4 * p.H + n0;
                 float hn[8];
 #pragma unroll
                 for (int u = 0; u < 8; u++) {
-                    const float4 z4 = *reinterpret_cast<const float4 *>(zin + 4 * u);
-                    const float zi = __uint_as_float(v[4 * u]) + z4.x, zf = __uint_as_float(v[4 * u + 1]) + z4.y;
-                    const float zg = __uint_as_float(v[4 * u + 2]) + z4.z, zo = __uint_as_float(v[4 * u + 3]) + z4.w;
-                    const float2 ch = lstm_cell_unit_f32(zi, zf, zg, zo, c[u]);
+                    const float zi = __uint_as_float(v[4 * u]) + z4[u].x, zf = __uint_as_float(v[4 * u + 1]) + z4[u].y;
+                    const float zg = __uint_as_float(v[4 * u + 2]) + z4[u].z, zo = __uint_as_float(v[4 * u + 3]) + z4[u].w;
+                    const float2 ch = lstm_cell_unit_f32_inline(zi, zf, zg, zo, c[u]);
                     c[u] = ch.x; hn[u] = ch.y;
                 }
                 const size_t o = row * p.H + unit0;
@@ -253,7 +263,7 @@ bool lstm_persistent_supported(const nb_handle_s *h, int T, int B, int H) {
     if (!h->encode_tiled || h->cc_major != 10 || !h->cooperative_launch) return false;
     if (T < 2 || B < 1 || B > 128 || (H % 32) != 0) return false;      // (a box of B rows: any B up to 128)
     const int ctas = 4 * H / LP_N;
-    const size_t smem = (size_t)(H / BLOCK_K) * LP_W_TILE + LP_STAGES * A_STAGE_BYTES + 1024 + 256;
+    const size_t smem = (size_t)(H / BLOCK_K) * LP_W_TILE + 2 * (A_STAGE_BYTES + (size_t)B * 128) + 1024 + 256;   // two stages at least
     return ctas <= h->sm_count && smem <= 227 * 1024;
 }
 
@@ -279,16 +289,22 @@ void lstm_persistent(nb_handle_s *h, const float *w_hi, const float *pre, float 
         cuuint32_t bx[3] = {(cuuint32_t)BLOCK_K, (cuuint32_t)LP_N, 1};
         cuuint32_t es[3] = {1, 1, 1};
         encode_tensor_map(h, &L->p.tm_w, w_hi, 3, dims, strides, bx, es);
-        cuuint64_t hdims[2] = {(cuuint64_t)H, (cuuint64_t)T * (cuuint64_t)B};
-        cuuint64_t hstrides[1] = {(cuuint64_t)H * 4};
-        cuuint32_t hbx[2] = {(cuuint32_t)BLOCK_K, (cuuint32_t)B};
-        cuuint32_t hes[2] = {1, 1};
-        encode_tensor_map(h, &L->p.tm_h, hr, 2, hdims, hstrides, hbx, hes);
+        // two K blocks per request when the second slice starts on the swizzle pattern's 1024-byte repeat
+        const int cbs = ((B % 8) == 0 && (H % (2 * BLOCK_K)) == 0) ? 2 : 1;
+        const int stage_bytes = (cbs - 1) * B * 128 + A_STAGE_BYTES;
+        const int w_bytes = (H / BLOCK_K) * LP_W_TILE;
+        const int stages = std::min(LP_STAGES, (227 * 1024 - 1024 - 256 - w_bytes) / stage_bytes);
+        cuuint64_t hdims[3] = {(cuuint64_t)BLOCK_K, (cuuint64_t)T * (cuuint64_t)B, (cuuint64_t)(H / BLOCK_K)};
+        cuuint64_t hstrides[2] = {(cuuint64_t)H * 4, (cuuint64_t)BLOCK_K * 4};
+        cuuint32_t hbx[3] = {(cuuint32_t)BLOCK_K, (cuuint32_t)B, (cuuint32_t)cbs};
+        cuuint32_t hes[3] = {1, 1, 1};
+        encode_tensor_map(h, &L->p.tm_h, hr, 3, hdims, hstrides, hbx, hes);
+        L->p.cbs = cbs; L->p.stages = stages; L->p.stage_bytes = stage_bytes;
         L->p.pre = pre; L->p.hr = hr; L->p.hr_w = hr; L->p.cell = cell; L->p.out = out;
         L->p.T = T; L->p.B = B; L->p.H = H; L->p.t_first = t_first;
         L->p.sync = h->d_grid_sync; L->p.status = h->d_status;
         L->grid = 4 * H / LP_N;
-        L->smem = (H / BLOCK_K) * LP_W_TILE + LP_STAGES * A_STAGE_BYTES + 1024 + 256;
+        L->smem = w_bytes + stages * stage_bytes + 1024 + 256;
         L->flops = 2.0 * (double)(T - t_first) * B * 4.0 * H * H;
         if (h->launch_cache.size() > 4096) h->launch_cache.clear();
         it = h->launch_cache.emplace(std::move(key), std::move(L)).first;
