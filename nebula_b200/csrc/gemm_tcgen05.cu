@@ -153,7 +153,10 @@ struct Cfg {
     static constexpr int STAGES = (196 * 1024) / STAGE_BYTES < 8 ? (196 * 1024) / STAGE_BYTES : 8;
     static constexpr int TMEM_COLS = 2 * BLOCK_N;
     static constexpr int OUT_STAGE_BYTES = BLOCK_M * 32 * 4;     // one 128 x 32 output slab
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 2 * OUT_STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+    static constexpr int LAYOUT_BYTES = STAGES * STAGE_BYTES + 2 * OUT_STAGE_BYTES + 256 /*barriers*/;
+    // all of the 227 KB a CTA may have: what the layout and its alignment leave over holds the epilogue's scale/shift values
+    static constexpr int SMEM_BYTES = 227 * 1024;
+    static_assert(LAYOUT_BYTES + 1024 <= SMEM_BYTES, "ring, staging buffers and barriers must fit");
 };
 
 // ------------------------------------------------------------------- kernel
@@ -182,6 +185,11 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
     uint64_t *acc_empty = acc_full + 2;       // epilogue -> MMA   [2]
     uint32_t *tmem_slot = (uint32_t *)(acc_empty + 2);
     volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
+    // per epilogue group: scale [BLOCK_N / 2] then shift [BLOCK_N / 2] of the columns of its slabs, if the alignment of
+    // the dynamic shared memory left room behind the barriers (it does when the base is 1024-byte aligned already)
+    float *aff_base = (float *)((uint8_t *)bars + 256);
+    const bool aff_smem = !THREE && !PROMOTE && p.e.shift != nullptr && p.e.lstm_H == 0 &&
+                          smem_raw + C::SMEM_BYTES >= (uint8_t *)(aff_base + 2 * BLOCK_N);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -403,6 +411,7 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
         float4 *slab1 = p.slab2_offset ? reinterpret_cast<float4 *>(smem + p.slab2_offset + grp * C::OUT_STAGE_BYTES) : slab0;
         const int stores_in_flight = p.slab2_offset ? 1 : 0;
         float4 *slab = slab0;
+        int aff_tile = -1;
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
@@ -414,6 +423,30 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
             const long row = ((long)n * p.OH + oh) * p.OW + ow;
             const EpiRow erow{r, row, row_ok, addend_row(p.e, row_ok, row, n, oh, ow)};
             const EpiBox ebox{p.bw, p.bh, p.bn, tw * p.bw, th * p.bh * halves, tn * p.bn + split * p.NB};
+            if (aff_smem && n_tile != aff_tile) {
+                // this group's scale/shift values for the tile column (its slabs are chunks grp, grp + 2, ...)
+                float *ga = aff_base + grp * BLOCK_N;
+                epilogue_bar_sync(bar_id);          // the previous column's values are no longer read
+                if (t < BLOCK_N / 2) {
+                    const int col = n_tile * BLOCK_N + (grp + 2 * (t >> 5)) * 32 + (t & 31);
+                    const bool in = col < ((p.e.N + 31) & ~31);     // the vectors are padded to a multiple of 32
+                    ga[t] = (in && p.e.scale) ? p.e.scale[col] : 1.0f;
+                    ga[BLOCK_N / 2 + t] = in ? p.e.shift[col] : 0.0f;
+                }
+                epilogue_bar_sync(bar_id);
+                aff_tile = n_tile;
+            }
+            if (erow.arow) {
+                // The addend (a residual tensor, the LSTM's input-side projection) comes from DRAM and each slab's
+                // 128 bytes of it are needed only once the accumulators are in registers: start this group's lines
+                // towards L2 now, while the tile's MMAs still run.
+#pragma unroll 1
+                for (int chunk = grp; chunk < BLOCK_N / 32; chunk += 2) {
+                    const int col0 = n_tile * BLOCK_N + chunk * 32;
+                    if (col0 >= p.e.addend_cols) break;
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(erow.arow + col0));
+                }
+            }
             if (!PROMOTE || p.parts == 1) {
                 if (!(ok = epilogue_all(mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status), bar_id))) break;
                 tc_fence_after();
@@ -445,7 +478,8 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
                         else if (chunk + 2 < BLOCK_N / 32 && col0 + 64 < p.e.N) next = taddr + 64;
                         else if (hf + 1 < halves) next = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * acc_cols + (hf + 1) * BLOCK_N + grp * 32);
                         epilogue_chunk<THREE>(p.e, &p.tm_y, &p.tm_yp, v, col0, hrow, hbox, slab, bar_id, store_thread, t, stores_in_flight,
-                                              [&] { if (next) { tmem_ld_32x32(next, v); loaded = true; } });
+                                              [&] { if (next) { tmem_ld_32x32(next, v); loaded = true; } },
+                                              aff_smem ? aff_base + grp * BLOCK_N + (chunk >> 1) * 32 : nullptr, BLOCK_N / 2);
                         slab = slab == slab0 ? slab1 : slab0;
                     }
                 }

@@ -229,6 +229,12 @@ __device__ __forceinline__ void umma_commit(uint64_t *bar) {
                  : "memory");
 }
 
+__device__ __forceinline__ float4 lds128(const float *p) {
+    float4 r;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(r.x), "=f"(r.y), "=f"(r.z), "=f"(r.w) : "r"(smem_u32(p)));
+    return r;
+}
+
 // Warp-wide (.sync.aligned): the warp is re-converged first, whatever branch its lanes came from.
 __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&v)[32]) {
     __syncwarp();
@@ -264,10 +270,32 @@ template <bool F64_CELL, class Staged>
 __device__ __forceinline__ void epilogue_chunk(const EpiParams &e, const CUtensorMap *tm_y, const CUtensorMap *tm_yp,
                                                uint32_t (&v)[32], int col0, const EpiRow &rw, const EpiBox &bx,
                                                float4 *slab, int bar_id, bool store_thread, int t, int stores_in_flight,
-                                               Staged &&staged) {
+                                               Staged &&staged, const float *aff = nullptr, int aff_shift = 0) {
     const bool full_cols = col0 + 32 <= e.N;
-    // affine part: folded batch-norm scale/shift + bias (vectors padded to a multiple of 32)
-    if (e.scale) {
+    // affine part: folded batch-norm scale/shift + bias (vectors padded to a multiple of 32).  `aff`: this slab's 32
+    // scale values in shared memory and its 32 shift values `aff_shift` floats further (the caller stages them once per
+    // tile column: read from global memory here, 8-16 loads sit on every slab's critical path)
+    if (aff) {
+        if (e.scale) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+                const float4 sc = lds128(aff + j), sh = lds128(aff + aff_shift + j);
+                v[j] = __float_as_uint(fmaf(__uint_as_float(v[j]), sc.x, sh.x));
+                v[j + 1] = __float_as_uint(fmaf(__uint_as_float(v[j + 1]), sc.y, sh.y));
+                v[j + 2] = __float_as_uint(fmaf(__uint_as_float(v[j + 2]), sc.z, sh.z));
+                v[j + 3] = __float_as_uint(fmaf(__uint_as_float(v[j + 3]), sc.w, sh.w));
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+                const float4 sh = lds128(aff + aff_shift + j);
+                v[j] = __float_as_uint(__uint_as_float(v[j]) + sh.x);
+                v[j + 1] = __float_as_uint(__uint_as_float(v[j + 1]) + sh.y);
+                v[j + 2] = __float_as_uint(__uint_as_float(v[j + 2]) + sh.z);
+                v[j + 3] = __float_as_uint(__uint_as_float(v[j + 3]) + sh.w);
+            }
+        }
+    } else if (e.scale) {
 #pragma unroll
         for (int j = 0; j < 32; j += 4) {
             const float4 sc = __ldg(reinterpret_cast<const float4 *>(e.scale + col0 + j));
