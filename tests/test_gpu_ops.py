@@ -267,7 +267,8 @@ def test_lstm(handle, mode, case):
     assert_close(out.cpu().numpy(), ref, mode, f"lstm {case}")
 
 
-@pytest.mark.parametrize("case", [(6, 16, 64, 64, False), (9, 64, 96, 256, True), (5, 128, 64, 1024, False)],
+@pytest.mark.parametrize("case", [(6, 16, 64, 64, False), (9, 64, 96, 256, True), (5, 128, 64, 1024, False),
+                                  (2, 8, 32, 96, False), (7, 5, 40, 32, False), (4, 100, 64, 160, True)],
                          ids=lambda c: "x".join(map(str, c)))
 def test_lstm_one_kernel_recurrence_is_bit_identical(handle, case, monkeypatch):
     """TF32 mode runs steps 1..T-1 as one cooperative kernel (weights resident in shared memory, a grid barrier per
