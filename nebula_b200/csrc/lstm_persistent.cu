@@ -14,7 +14,6 @@
 // then issues fence.proxy.async before its first copy of the step.  (A first version read h with ld.global.cg from
 // 128 threads: correct, but 63 us per step, three times slower than a launch per step.)  The results are bit-identical
 // to the per-step path (same K order, same fp32 cell arithmetic).
-#include <cooperative_groups.h>
 #include <cstring>
 
 #include "tc_common.cuh"
@@ -36,8 +35,7 @@ struct LstmPParams {
     int cbs;                    // K blocks per ring stage and TMA request (2 when B % 8 == 0 and H % 64 == 0)
     int stages, stage_bytes;    // ring geometry: a stage holds cbs slices of B rows and the 128-row window of the last
     const float *pre;           // [T][B][4H] input-side pre-activations (biases included), columns [unit][i,f,g,o]
-    const float *hr;            // [T][B][H] rounded hidden states: step t reads [t-1], writes [t]
-    float *hr_w;                // the same tensor, for writing
+    float *hr_w;                // [T][B][H] rounded hidden states: step t writes [t]; step t + 1 reads it through tm_h
     float *cell, *out;          // [T][B][H]
     int T, B, H;
     int t_first;                // first step this kernel runs (the steps before it are in cell/out/hr already)
@@ -300,7 +298,7 @@ void lstm_persistent(nb_handle_s *h, const float *w_hi, const float *pre, float 
         cuuint32_t hes[3] = {1, 1, 1};
         encode_tensor_map(h, &L->p.tm_h, hr, 3, hdims, hstrides, hbx, hes);
         L->p.cbs = cbs; L->p.stages = stages; L->p.stage_bytes = stage_bytes;
-        L->p.pre = pre; L->p.hr = hr; L->p.hr_w = hr; L->p.cell = cell; L->p.out = out;
+        L->p.pre = pre; L->p.hr_w = hr; L->p.cell = cell; L->p.out = out;
         L->p.T = T; L->p.B = B; L->p.H = H; L->p.t_first = t_first;
         L->p.sync = h->d_grid_sync; L->p.status = h->d_status;
         L->grid = 4 * H / LP_N;
