@@ -175,7 +175,13 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
     const int stage_bytes = p.stage_bytes;
     const int halves = (THREE || PROMOTE || BLOCK_N > 128) ? 1 : p.halves;
     const int acc_cols = halves * BLOCK_N;              // TMEM columns of one accumulator set
-    const uint32_t tmem_cols = (uint32_t)(C::TMEM_COLS * halves);
+    // 3xTF32 with several partial sums per tile: the two small cross terms (a_lo*b_hi + a_hi*b_lo) accumulate in a set of
+    // columns of their own for the whole tile (their magnitude is 2^-11 of the product's, so what the tensor core's
+    // truncating accumulation loses on them is nothing), one set per tile parity behind the two product accumulators.
+    // Only the hi*hi chain is then promoted, and a K block adds 4 MMAs to it instead of 12: a third of the promotions
+    // for the same chain length.
+    const bool cross_cols = THREE && p.parts > 1;
+    const uint32_t tmem_cols = (uint32_t)(C::TMEM_COLS * (THREE ? 2 : halves));
     uint8_t *out_stage = smem + STAGES * C::STAGE_BYTES;      // 2 x [128 rows][32 floats], 128B-swizzled
     uint64_t *bars = (uint64_t *)(out_stage + 2 * C::OUT_STAGE_BYTES);
     uint64_t *full = bars;                    // TMA -> (splitter or MMA)
@@ -319,6 +325,7 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
         uint32_t phase = 0;
         int acc = 0;
         uint32_t acc_phase = 0;
+        int tile_parity = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
             if (!(ok = mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag, p.status))) break;
@@ -352,6 +359,8 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
             }
             const int ksplit = p.k_splits > 1 ? tile % p.k_splits : 0;
             const int tile_kb = min(p.kb_per_split, p.num_k_blocks - ksplit * p.kb_per_split);
+            const uint32_t x_tmem = tmem_base + (uint32_t)(2 * BLOCK_N + tile_parity * BLOCK_N);    // cross terms of this tile
+            tile_parity ^= 1;
             for (int kb = 0; kb < tile_kb; kb += cbs, kb_in_part += cbs) {
                 if (kb_in_part == p.kb_per_part) {
                     // hand this partial sum to the epilogue warps and restart in the other accumulator
@@ -376,9 +385,15 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
                             if (THREE) {
                                 const uint64_t da_lo = smem_desc(b_lo + (C::B_STAGE_BYTES >> 4) + 2 * k);
                                 const uint64_t db_lo = smem_desc(b_lo + ((C::B_STAGE_BYTES + A_STAGE_BYTES) >> 4) + 2 * k);
-                                umma_tf32(d_tmem, da_lo, db, idesc, (kb_in_part | k) != 0);
-                                umma_tf32(d_tmem, da, db_lo, idesc, 1);
-                                umma_tf32(d_tmem, da, db, idesc, 1);
+                                if (cross_cols) {
+                                    umma_tf32(x_tmem, da_lo, db, idesc, (kb | k) != 0);
+                                    umma_tf32(x_tmem, da, db_lo, idesc, 1);
+                                    umma_tf32(d_tmem, da, db, idesc, (kb_in_part | k) != 0);
+                                } else {
+                                    umma_tf32(d_tmem, da_lo, db, idesc, (kb_in_part | k) != 0);
+                                    umma_tf32(d_tmem, da, db_lo, idesc, 1);
+                                    umma_tf32(d_tmem, da, db, idesc, 1);
+                                }
                             } else {
                                 umma_tf32(d_tmem, da, db, idesc, (kb_in_part | c | k) != 0);
                             }
@@ -412,6 +427,7 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
         const int stores_in_flight = p.slab2_offset ? 1 : 0;
         float4 *slab = slab0;
         int aff_tile = -1;
+        int epi_tile_parity = 0;
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
@@ -491,6 +507,8 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
                 uint32_t sum[CH][32];
                 const int tile_kb = min(p.kb_per_split, p.num_k_blocks - split * p.kb_per_split);
                 const int parts = (tile_kb + p.kb_per_part - 1) / p.kb_per_part;
+                const uint32_t x_cols = (uint32_t)(2 * BLOCK_N + epi_tile_parity * BLOCK_N);
+                epi_tile_parity ^= 1;
                 for (int part = 0; part < parts && ok; part++) {
                     if (!(ok = epilogue_all(mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status), bar_id))) break;
                     tc_fence_after();
@@ -505,6 +523,13 @@ gemm_tf32_tcgen05_kernel(const __grid_constant__ TcParams p) {
 #pragma unroll
                                 for (int j = 0; j < 32; j++) sum[ci][j] = v[j];
                             } else {
+#pragma unroll
+                                for (int j = 0; j < 32; j++)
+                                    sum[ci][j] = __float_as_uint(__uint_as_float(sum[ci][j]) + __uint_as_float(v[j]));
+                            }
+                            if (cross_cols && part == parts - 1) {      // the tile's cross terms: complete with its last MMAs
+                                tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + x_cols + (uint32_t)(chunk * 32), v);
+                                tmem_ld_wait();
 #pragma unroll
                                 for (int j = 0; j < 32; j++)
                                     sum[ci][j] = __float_as_uint(__uint_as_float(sum[ci][j]) + __uint_as_float(v[j]));
@@ -866,10 +891,10 @@ std::unique_ptr<TcLaunch> build_launch(nb_handle_s *h, const GemmArgs &a, bool t
     }
     p.n_tiles = (a.N + block_n - 1) / block_n;
     p.m_fastest = (!a.a_is_conv && !gather && (size_t)a.N * a.Kc * 4 > ((size_t)48 << 20)) ? 1 : 0;
-    // accumulation chains of at most 512 (TF32) / 32 (3xTF32) K elements in the tensor core: every accumulating MMA
-    // truncates the running sum (a shrink of about 6e-8 per step that adds up layer after layer); a 3xTF32 K block
-    // is 12 MMAs, 11 of them accumulating
-    p.kb_per_part = !promote ? p.kb_per_split : (three_pass ? 1 : 16);
+    // accumulation chains of at most 512 K elements (TF32) / 12 MMAs (3xTF32) in the tensor core: every accumulating MMA
+    // truncates the running sum (a shrink of about 6e-8 per step that adds up layer after layer).  A 3xTF32 K block is
+    // 12 MMAs, of which only the 4 hi*hi ones go into the promoted chain (the cross terms have columns of their own)
+    p.kb_per_part = !promote ? p.kb_per_split : (three_pass ? 3 : 16);
     p.parts = (p.kb_per_split + p.kb_per_part - 1) / p.kb_per_part;
 
     // two K blocks per ring stage: narrow tiles (<= 128 filters) of a convolution whose channel slices pair up, a
