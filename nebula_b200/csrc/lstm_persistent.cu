@@ -103,7 +103,7 @@ __global__ void __launch_bounds__(LP_THREADS, 1) lstm_persistent_kernel(const __
             mbar_expect_tx(w_full, (uint32_t)(KB * LP_W_TILE));
             for (int kb = 0; kb < KB; kb++) tma_load_3d(w_smem + kb * LP_W_TILE, &p.tm_w, w_full, kb * BLOCK_K, n0, 0);
             ok = mbar_wait(w_full, 0, abort_flag, p.status);
-            constexpr uint32_t idesc = make_idesc(BLOCK_M, LP_N);
+            const uint32_t idesc = p.B <= 64 ? make_idesc(64, LP_N) : make_idesc(BLOCK_M, LP_N);     // 64-row MMAs for small batches
             int stage = 0;
             uint32_t phase = 0;
             for (int t = p.t_first; t < p.T && ok; t++) {
@@ -154,14 +154,18 @@ __global__ void __launch_bounds__(LP_THREADS, 1) lstm_persistent_kernel(const __
         __syncwarp();
     } else {
         // ------------------------------------------------ epilogue of every step, then the grid barrier
-        const int tid = threadIdx.x;                        // 0..127: row `tid` of the tile
-        const bool row_ok = tid < p.B;
+        const int tid = threadIdx.x;                        // 0..127
+        // the batch row whose accumulators this thread's TMEM lane holds: lane = row for a 128-row MMA; a 64-row MMA
+        // puts 16 rows into the first 16 lanes of each 32-lane quarter
+        const int lane = tid & 31;
+        const int brow = p.B <= 64 ? (lane < 16 ? 16 * warp + lane : 1 << 20) : tid;
+        const bool row_ok = brow < p.B;
         const int unit0 = n0 >> 2;                          // first hidden unit of this CTA (8 of them)
         float c[8];
 #pragma unroll
         for (int u = 0; u < 8; u++) c[u] = 0.0f;
         if (row_ok && p.t_first > 0) {
-            const float *cp = p.cell + ((size_t)(p.t_first - 1) * p.B + tid) * p.H + unit0;
+            const float *cp = p.cell + ((size_t)(p.t_first - 1) * p.B + brow) * p.H + unit0;
             const float4 lo = *reinterpret_cast<const float4 *>(cp), hi = *reinterpret_cast<const float4 *>(cp + 4);
             c[0] = lo.x; c[1] = lo.y; c[2] = lo.z; c[3] = lo.w; c[4] = hi.x; c[5] = hi.y; c[6] = hi.z; c[7] = hi.w;
         }
@@ -170,7 +174,7 @@ __global__ void __launch_bounds__(LP_THREADS, 1) lstm_persistent_kernel(const __
             // gates of this CTA's 8 units for row `tid`; threads only leave the loop together, at the votes, so that
             // none is left alone at a barrier
             // the input-side pre-activations of this step come from DRAM: fetched while the MMAs run
-            const size_t row = (size_t)t * p.B + tid;
+            const size_t row = (size_t)t * p.B + brow;
             float4 z4[8];
             if (row_ok) {
                 const float4 *zin = reinterpret_cast<const float4 *>(p.pre + row * 4 * p.H + n0);
